@@ -9,7 +9,12 @@ a *cache entry*; entries with the same need form a *group* with storage of its o
                it grows and gives them back when it ends; a reused page is not cleared, because
                no kernel reads a position beyond a sequence's length.
   state group  a float32 tensor of fixed shape per (entry, slot), zeroed when the slot is
-               taken.  The Llama decoder has none; a mixer with a recurrent state would.
+               taken.  The Llama decoder has none; a mixer with a recurrent state has.
+
+A layer run that keeps several things (a convolution's tail and a recurrence's state; keys and
+values beside a recurrent state; a block arrangement's own state beside its mixer's) names them
+in a NeedSet; each named need joins the group of its kind, and the layer run's entry is a
+`CompositeEntry` that answers `entry[name]`.
 
 Lengths are per slot and shared by all groups.  Everything a step needs on the device about
 the cache (the batch's rows of the page tables) is packed by the engine into the step's
@@ -18,7 +23,7 @@ metadata; this class owns the storage and the bookkeeping.
 import numpy as np
 import torch
 
-from ..parts.base import KVNeed, StateNeed
+from ..parts.base import KVNeed, NeedSet, StateNeed
 from .slots import CacheError, FreeList
 
 PAGE = 64
@@ -46,6 +51,27 @@ class CacheEntry:
     def state(self):
         return self.group.state[self.index]
 
+    @property
+    def pooled_k(self):
+        return self.group.pooled_k[self.index]
+
+    @property
+    def pooled_v(self):
+        return self.group.pooled_v[self.index]
+
+
+class CompositeEntry:
+    """The entries of a layer run that keeps several things, by the names of its NeedSet."""
+
+    def __init__(self, parts):
+        self.parts = dict(parts)
+
+    def __getitem__(self, name):
+        return self.parts[name]
+
+    def get(self, name, default=None):
+        return self.parts.get(name, default)
+
 
 class KVGroup:
     """Keys and values of the schedule entries with one need.  With `need.window` the group keeps, per sequence, only
@@ -67,14 +93,23 @@ class KVGroup:
         self.n_held = np.zeros(n_slots, dtype=np.int32)
         self.low = np.zeros(n_slots, dtype=np.int32)      # a sequence holds the pages low .. low + n_held - 1
         self.version = 0                                  # counts changes of the table (a step's metadata is patched when it moved)
-        self.k = self.v = None
+        self.k = self.v = self.pooled_k = self.pooled_v = None
+        self.v_head_dim = need.v_head_dim or need.head_dim
+        self.pool_block = need.pool                        # positions per pooled block (None: no pooled rows)
+        if self.pool_block is not None and self.pool_block < 1:
+            raise CacheError(f"pooled blocks of {self.pool_block} positions")
+        self.pooled_rows = -(-PAGE // self.pool_block) if self.pool_block else 0     # block ends that fall into one page, at most
         if device is not None:
-            shape = (n_entries, n_pages, need.n_kv_heads, PAGE, need.head_dim)
-            self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape, dtype=dtype, device=device)
+            self.k = torch.zeros((n_entries, n_pages, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
+            self.v = torch.zeros((n_entries, n_pages, need.n_kv_heads, PAGE, self.v_head_dim), dtype=dtype, device=device)
+            if self.pool_block:
+                self.pooled_k = torch.zeros((n_entries, n_pages, need.n_kv_heads, self.pooled_rows, need.head_dim), dtype=torch.float32, device=device)
+                self.pooled_v = torch.zeros((n_entries, n_pages, need.n_kv_heads, self.pooled_rows, self.v_head_dim), dtype=torch.float32, device=device)
 
     def bytes_per_token(self, itemsize):
-        return 2 * self.n_entries * self.need.n_kv_heads * self.need.head_dim * itemsize
+        per_row = self.need.head_dim + self.v_head_dim
+        pooled = self.pooled_rows * per_row * 4 / PAGE
+        return int(self.n_entries * self.need.n_kv_heads * (per_row * itemsize + pooled))
 
     def first_page(self, position):
         """The first page that the token at `position` sees a key of."""
@@ -158,14 +193,27 @@ class SequenceCache:
         self.length = np.zeros(self.n_slots, dtype=np.int64)
         self.dtype, self.device = dtype, device
         self.groups, self.entries = [], []
-        windowed = any(isinstance(n, KVNeed) and n.window is not None for n in needs)
+        def plain(need):
+            if isinstance(need, NeedSet):
+                for _, sub in need.items:
+                    yield from plain(sub)
+            elif need is not None:
+                yield need
+        windowed = any(isinstance(n, KVNeed) and n.window is not None for need in needs for n in plain(need))
         # with a windowed group, steps are cut so that a sequence brings at most `piece_tokens` tokens at a time: what
         # such a group must hold per sequence is then the window and one piece, whatever the prompt's length
         self.piece_tokens = int(piece_tokens or self.PIECE_TOKENS) if windowed else None
         by_need = {}
+
+        def flatten(path, need):
+            """(path, need) of every plain need under `need`; a path is the schedule index and the names below it."""
+            if isinstance(need, NeedSet):
+                for name, sub in need.items:
+                    flatten(path + (name,), sub)
+            elif need is not None:
+                by_need.setdefault(need, []).append(path)
         for i, need in enumerate(needs):
-            if need is not None:
-                by_need.setdefault(need, []).append(i)
+            flatten((i,), need)
         where = {}
         for need, idxs in by_need.items():
             gid = len(self.groups)
@@ -180,7 +228,11 @@ class SequenceCache:
             self.groups.append(g)
             for j, i in enumerate(idxs):
                 where[i] = CacheEntry(g, j)
-        self.entries = [where.get(i) for i in range(len(needs))]
+        def entry_of(path, need):
+            if isinstance(need, NeedSet):
+                return CompositeEntry((name, entry_of(path + (name,), sub)) for name, sub in need.items)
+            return where.get(path)
+        self.entries = [entry_of((i,), need) for i, need in enumerate(needs)]
         self.kv_groups = [g for g in self.groups if isinstance(g, KVGroup)]
         self.state_groups = [g for g in self.groups if isinstance(g, StateGroup)]
 
@@ -282,7 +334,8 @@ class SequenceCache:
     def storage_bytes(self):
         total = 0
         for g in self.groups:
-            for t in (getattr(g, "k", None), getattr(g, "v", None), getattr(g, "state", None)):
+            for t in (getattr(g, "k", None), getattr(g, "v", None), getattr(g, "state", None), getattr(g, "pooled_k", None),
+                      getattr(g, "pooled_v", None)):
                 if t is not None:
                     total += t.numel() * t.element_size()
         return total
@@ -292,6 +345,8 @@ class SequenceCache:
         lines = [f"{self.n_slots} slots, {self.storage_bytes() / 1e6:.2f} MB"]
         for g in self.kv_groups:
             win = f", the last {g.window} keys of a sequence" if g.window is not None else ""
+            if g.pool_block:
+                win += f", a pooled row per {g.pool_block} positions"
             lines.append(f"  keys/values of {g.n_entries} layer run(s): {g.need.n_kv_heads} heads of {g.need.head_dim}{win}, {g.n_pages} pages "
                          f"of {PAGE} tokens, {g.bytes_per_token(torch.empty(0, dtype=self.dtype).element_size())} B a token")
         for g in self.state_groups:

@@ -44,13 +44,16 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: its arrangement and its four parts.  `prefix` starts its tensors' names."""
+    """One layer: its arrangement and its four parts.  `prefix` starts its tensors' names.  `ffn` (and its norm)
+    may be None for an arrangement that takes a layer without a feed-forward; `options` holds what the arrangement
+    itself wants to know (a tensor's name, a constant)."""
     prefix: str
     block: str
     mixer: PartSpec
     mixer_norm: PartSpec
-    ffn: PartSpec
-    ffn_norm: PartSpec
+    ffn: Optional[PartSpec]
+    ffn_norm: Optional[PartSpec]
+    options: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration class.
 
-`architectures[0]` of config.json picks the entry; a config.json without that key falls back
-to `model_type`.  An architecture registers a class with two things: `from_dict(dict)` that
+`architectures[0]` of config.json picks the entry (or `architecture`, a single name); a
+config.json without these keys falls back to `model_type`.  An architecture registers a class with two things: `from_dict(dict)` that
 reads and checks its own keys, and `plan()` that returns the ModelPlan.
 """
 import json
@@ -32,6 +32,8 @@ def registered_architectures():
 
 def config_class_for(config_dict):
     archs = config_dict.get("architectures")
+    if not archs and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]
     if archs:
         name = archs[0]
         if name in _ARCHITECTURES:

@@ -1,0 +1,273 @@
+// Sliding-window attention with pooled blocks behind the window, over the paged cache.
+//
+// A token at position i sees the keys j with 0 <= i - j < window, and one pooled key and value per block of P
+// consecutive positions that lies wholly before the window (block b = positions bP .. bP + P - 1 is seen iff
+// bP + P - 1 <= i - window).  A pooled key (value) is the mean of the block's P keys (values) as the cache holds
+// them.  Tokens and blocks share one softmax.
+//
+// Cache layout: keys [page][kv_head][PAGE][dk], values [page][kv_head][PAGE][dv] in the compute type, as the other
+// attention kernels keep them; pooled keys and values in float32, [page][kv_head][R][dk or dv], where a block's
+// row lives in the page that holds the block's LAST position e = bP + P - 1: page e / PAGE, row b - (PAGE * (e / PAGE)) / P
+// (R = ceil(PAGE / P) rows a page are enough: that many block ends fall into one page at most).
+//
+// Three kernels: (1) bias, partial rotation, per-head unit RMS norm of q and k, append of k and v; (2) the pooled
+// rows of the blocks that the step's tokens complete; (3) attention.  Scores, softmax, norms, angles: float32.
+#include "common.cuh"
+
+namespace edgelm {
+
+constexpr int PW_WARPS = 4;
+
+// qkv: [tokens][H dk + G dk + G dv] float32 (the stacked projection), biases float32 (may be null).
+// The first `rot` dimensions of each query and key head are rotated: (u, v) = (x[i], x[i + rot/2]) becomes
+// (u cos a - v sin a, v cos a + u sin a), a = position * freq[i]; then the head is divided by its root mean square.
+template <typename T>
+__global__ void __launch_bounds__(PW_WARPS * 32)
+qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, T* __restrict__ q_out,
+                           const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq,
+                           const int32_t* __restrict__ page_table, int table_stride, int n_pages, T* __restrict__ kcache,
+                           T* __restrict__ vcache, int H, int G, int dk, int dv, int rot, const float* __restrict__ freq,
+                           float eps, int unit_norm, int* __restrict__ err) {
+  extern __shared__ float stage[];   // PW_WARPS rows of dk floats
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = tok_pos[t];
+  if (pos < 0) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_POSITION_RANGE);
+    return;
+  }
+  const int page = page_table[(size_t)tok_seq[t] * table_stride + pos / PAGE];
+  if (page < 0 || page >= n_pages) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_PAGE_RANGE);
+    return;
+  }
+  const int in_page = pos % PAGE, half = rot >> 1;
+  const int ld = H * dk + G * dk + G * dv;
+  const float* row = qkv + (size_t)t * ld;
+  float* sh = stage + warp * dk;
+  const float fpos = (float)pos;
+  for (int head = warp; head < H + G; head += PW_WARPS) {   // query heads, then key heads
+    const float* src = row + (size_t)head * dk;
+    const float* b = bias ? bias + (size_t)head * dk : nullptr;
+    for (int i = lane; i < dk; i += 32) sh[i] = src[i] + (b ? b[i] : 0.f);
+    __syncwarp();
+    float ss = 0.f;
+    float val[8];
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const int i = lane + 32 * m;
+      float x = 0.f;
+      if (i < dk) {
+        x = sh[i];
+        if (i < rot) {
+          const int f = i < half ? i : i - half;
+          float sn, cs;
+          sincosf(fpos * freq[f], &sn, &cs);
+          x = i < half ? sh[i] * cs - sh[i + half] * sn : sh[i] * cs + sh[i - half] * sn;
+        }
+      }
+      val[m] = x;
+      ss = fmaf(x, x, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = unit_norm ? 1.0f / sqrtf(ss / (float)dk + eps) : 1.0f;
+    T* dst = head < H ? q_out + ((size_t)t * H + head) * dk : kcache + (((size_t)page * G + (head - H)) * PAGE + in_page) * dk;
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+      const int i = lane + 32 * m;
+      if (i < dk) dst[i] = from_f32<T>(val[m] * inv);
+    }
+    __syncwarp();
+  }
+  const float* vrow = row + (size_t)(H + G) * dk;
+  const float* vb = bias ? bias + (size_t)(H + G) * dk : nullptr;
+  for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+    const int g = i / dv, j = i - g * dv;
+    vcache[(((size_t)page * G + g) * PAGE + in_page) * dv + j] = from_f32<T>(vrow[i] + (vb ? vb[i] : 0.f));
+  }
+}
+
+// The pooled rows of the blocks that end at a token of this step.
+template <typename T>
+__global__ void pool_blocks_kernel(const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq,
+                                   const int32_t* __restrict__ page_table, int table_stride, int n_pages,
+                                   const T* __restrict__ kcache, const T* __restrict__ vcache, float* __restrict__ pk,
+                                   float* __restrict__ pv, int G, int dk, int dv, int P, int R, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  if (pos < 0 || (pos + 1) % P != 0) return;
+  const int b = (pos + 1) / P - 1;
+  const int32_t* table = page_table + (size_t)tok_seq[t] * table_stride;
+  const int dst_page = table[pos / PAGE];
+  if (dst_page < 0 || dst_page >= n_pages) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_PAGE_RANGE);
+    return;
+  }
+  const int rowi = b - (PAGE * (pos / PAGE)) / P;
+  const float invP = 1.0f / (float)P;
+  for (int i = threadIdx.x; i < G * (dk + dv); i += blockDim.x) {
+    const bool is_k = i < G * dk;
+    const int e = is_k ? i : i - G * dk, d = is_k ? dk : dv;
+    const int g = e / d, c = e - g * d;
+    const T* base = is_k ? kcache : vcache;
+    float acc = 0.f;
+    for (int j = 0; j < P; ++j) {
+      const int p = b * P + j;
+      const int page = table[p / PAGE];
+      if (page < 0 || page >= n_pages) continue;   // (flagged by the append of that token's step)
+      acc += to_f32(base[(((size_t)page * G + g) * PAGE + p % PAGE) * d + c]);
+    }
+    float* dst = is_k ? pk : pv;
+    dst[(((size_t)dst_page * G + g) * R + rowi) * d + c] = acc * invP;
+  }
+}
+
+// One warp per (token, query head).  Keys are walked 32 at a time, a lane a key: pooled blocks first, then the
+// window's tokens; online softmax in float32; the weighted values are gathered with the lanes over the value's
+// dimensions.  q [tokens][H dk], out [tokens][H dv].
+template <typename T>
+__global__ void __launch_bounds__(PW_WARPS * 32)
+pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
+                          const float* __restrict__ pk, const float* __restrict__ pv, const int32_t* __restrict__ tok_pos,
+                          const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table, int table_stride,
+                          int n_pages, int H, int G, int dk, int dv, float scale, int window, int P, int R) {
+  extern __shared__ float qs[];   // PW_WARPS rows of dk floats
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h = blockIdx.y * PW_WARPS + warp;
+  if (h >= H) return;
+  const int pos = tok_pos[t];
+  if (pos < 0) return;
+  const int g = h / (H / G);
+  const int32_t* table = page_table + (size_t)tok_seq[t] * table_stride;
+  float* qh = qs + warp * dk;
+  for (int i = lane; i < dk; i += 32) qh[i] = to_f32(q[((size_t)t * H + h) * dk + i]) * scale;
+  __syncwarp();
+  const int lo = max(0, pos - window + 1);
+  const int n_blocks = (P > 0 && pos - window >= 0) ? (pos - window + 1) / P : 0;
+  const int total = n_blocks + (pos - lo + 1);
+  float m = -INFINITY, l = 0.f;
+  float o[8];
+#pragma unroll
+  for (int r = 0; r < 8; ++r) o[r] = 0.f;
+  for (int e0 = 0; e0 < total; e0 += 32) {
+    const int e = e0 + lane;
+    float sc = -INFINITY;
+    long long voff = -1;          // row offset into the value storage; pooled rows are marked by bit 62
+    if (e < total) {
+      if (e < n_blocks) {
+        const int end = e * P + P - 1;
+        const int page = table[end / PAGE];
+        if (page >= 0 && page < n_pages) {
+          const size_t rowi = ((size_t)page * G + g) * R + (e - (PAGE * (end / PAGE)) / P);
+          const float* kr = pk + rowi * dk;
+          float acc = 0.f;
+          for (int i = 0; i < dk; ++i) acc = fmaf(qh[i], kr[i], acc);
+          sc = acc;
+          voff = (long long)(rowi * dv) | (1ll << 62);
+        }
+      } else {
+        const int p = lo + (e - n_blocks);
+        const int page = table[p / PAGE];
+        if (page >= 0 && page < n_pages) {
+          const size_t rowi = ((size_t)page * G + g) * PAGE + p % PAGE;
+          const T* kr = kcache + rowi * dk;
+          float acc = 0.f;
+          for (int i = 0; i < dk; ++i) acc = fmaf(qh[i], to_f32(kr[i]), acc);
+          sc = acc;
+          voff = (long long)(rowi * dv);
+        }
+      }
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    if (m_new == -INFINITY) continue;
+    const float w = sc == -INFINITY ? 0.f : expf(sc - m_new);
+    const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+    l = l * corr + warp_sum(w);
+    m = m_new;
+#pragma unroll
+    for (int r = 0; r < 8; ++r) o[r] *= corr;
+    const int n_here = min(32, total - e0);
+    for (int j = 0; j < n_here; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, w, j);
+      const long long vo = __shfl_sync(0xffffffffu, voff, j);
+      if (vo < 0) continue;
+      if (vo >> 62 & 1) {
+        const float* vr = pv + (vo & ~(1ll << 62));
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (lane + 32 * r < dv) o[r] = fmaf(wj, vr[lane + 32 * r], o[r]);
+      } else {
+        const T* vr = vcache + vo;
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+          if (lane + 32 * r < dv) o[r] = fmaf(wj, to_f32(vr[lane + 32 * r]), o[r]);
+      }
+    }
+  }
+  const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+  for (int r = 0; r < 8; ++r)
+    if (lane + 32 * r < dv) out[((size_t)t * H + h) * dv + lane + 32 * r] = from_f32<T>(o[r] * inv);
+}
+
+}  // namespace edgelm
+
+using namespace edgelm;
+
+extern "C" int edgelm_qk_rope_norm_append(const float* qkv, const float* bias, void* q_out, int dtype, const int32_t* tok_pos,
+                                          const int32_t* tok_seq, const int32_t* page_table, int table_stride, int n_pages,
+                                          void* kcache, void* vcache, int n_tokens, int H, int G, int dk, int dv, int rot,
+                                          const float* freq, float eps, int unit_norm, int* err, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && H > 0 && G > 0 && H % G == 0, "qk_rope_norm_append: %d query heads over %d key/value heads", H, G);
+  EL_REFUSE(dk >= 1 && dk <= 256 && dv >= 1 && dv <= 256, "qk_rope_norm_append: head sizes %d / %d are not taken (1 to 256)", dk, dv);
+  EL_REFUSE(rot >= 0 && rot <= dk && rot % 2 == 0, "qk_rope_norm_append: %d rotated dimensions of %d", rot, dk);
+  const size_t smem = (size_t)PW_WARPS * dk * sizeof(float);
+  if (dtype == DT_F32)
+    qk_rope_norm_append_kernel<float><<<n_tokens, PW_WARPS * 32, smem, stream>>>(qkv, bias, (float*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
+                                                                              (float*)kcache, (float*)vcache, H, G, dk, dv, rot, freq, eps, unit_norm, err);
+  else if (dtype == DT_BF16)
+    qk_rope_norm_append_kernel<__nv_bfloat16><<<n_tokens, PW_WARPS * 32, smem, stream>>>(qkv, bias, (__nv_bfloat16*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
+                                                                                      (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, freq, eps, unit_norm, err);
+  else
+    EL_REFUSE(false, "qk_rope_norm_append: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("qk_rope_norm_append");
+  return 0;
+}
+
+extern "C" int edgelm_pool_blocks(const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table, int table_stride,
+                                  int n_pages, const void* kcache, const void* vcache, int dtype, float* pk, float* pv,
+                                  int n_tokens, int G, int dk, int dv, int P, int R, int* err, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && G > 0 && dk > 0 && dv > 0 && P >= 1 && R == (PAGE + P - 1) / P, "pool_blocks: bad sizes (block %d, rows a page %d)", P, R);
+  if (dtype == DT_F32)
+    pool_blocks_kernel<float><<<n_tokens, 128, 0, stream>>>(tok_pos, tok_seq, page_table, table_stride, n_pages, (const float*)kcache, (const float*)vcache, pk, pv, G, dk, dv, P, R, err);
+  else if (dtype == DT_BF16)
+    pool_blocks_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>(tok_pos, tok_seq, page_table, table_stride, n_pages, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, pk, pv, G, dk, dv, P, R, err);
+  else
+    EL_REFUSE(false, "pool_blocks: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("pool_blocks");
+  return 0;
+}
+
+extern "C" int edgelm_pooled_window_attn(const void* q, void* out, const void* kcache, const void* vcache, int dtype, const float* pk,
+                                         const float* pv, const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table,
+                                         int table_stride, int n_pages, int n_tokens, int H, int G, int dk, int dv, float scale,
+                                         int window, int P, int R, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && H > 0 && G > 0 && H % G == 0, "pooled_window_attn: %d query heads over %d key/value heads", H, G);
+  EL_REFUSE(dk >= 1 && dk <= 256 && dv >= 1 && dv <= 256, "pooled_window_attn: head sizes %d / %d are not taken (1 to 256)", dk, dv);
+  EL_REFUSE(window >= 1 && P >= 0 && (P == 0 || R == (PAGE + P - 1) / P), "pooled_window_attn: window %d, block %d, rows a page %d", window, P, R);
+  const dim3 grid(n_tokens, (H + PW_WARPS - 1) / PW_WARPS), block(PW_WARPS * 32);
+  const size_t smem = (size_t)PW_WARPS * dk * sizeof(float);
+  if (dtype == DT_F32)
+    pooled_window_attn_kernel<float><<<grid, block, smem, stream>>>((const float*)q, (float*)out, (const float*)kcache, (const float*)vcache, pk, pv, tok_pos,
+                                                                    tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, window, P, R);
+  else if (dtype == DT_BF16)
+    pooled_window_attn_kernel<__nv_bfloat16><<<grid, block, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
+                                                                            (const __nv_bfloat16*)vcache, pk, pv, tok_pos, tok_seq, page_table, table_stride,
+                                                                            n_pages, H, G, dk, dv, scale, window, P, R);
+  else
+    EL_REFUSE(false, "pooled_window_attn: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("pooled_window_attn");
+  return 0;
+}

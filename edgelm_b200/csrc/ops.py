@@ -444,3 +444,151 @@ def read_error_word(err):
         err.zero_()
         raise KernelError("a kernel reported: " + "; ".join(what))
 
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Mixers with a fixed-size state (recurrent.cu) and the sliding-window attention with pooled blocks (attention_pooled.cu).
+# `seq_tok0`: int32 [n_seqs + 1], the packed row of each sequence's first token, closed by the step's token count;
+# `seq_slot`: the row of each sequence's state.  States are float32 tensors [slots, ...].
+
+def _f32(t, name):
+    _need(t.dtype == torch.float32 and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous float32 CUDA tensor")
+
+
+def shift_mix(inp, state, mu, out, tok_seq, seq_tok0, seq_slot):
+    """out[m, t] = a + (prev - a) * mu[m] with a = inp[t] and prev the row before it, or the sequence's state row for
+    the first token that the sequence brings to this step.  inp [T, D] float32 or bfloat16; mu [M, D]; out [M, T, D]."""
+    T, D = inp.shape
+    M = mu.shape[0]
+    _f32(state, "state"); _f32(mu, "mu")
+    _need(inp.is_contiguous() and out.is_contiguous() and out.shape == (M, T, D) and mu.shape == (M, D) and state.shape[1] == D, "shift_mix: shapes")
+    for t, n in ((tok_seq, "tok_seq"), (seq_tok0, "seq_tok0"), (seq_slot, "seq_slot")):
+        _i32(t, n)
+    _check(lib().edgelm_shift_mix(_p(inp), _dt(inp), _p(state), _p(mu), _p(out), _dt(out), _p(tok_seq), _p(seq_tok0), _p(seq_slot),
+                                  T, D, M, _stream()))
+
+
+def save_last_rows(inp, state, seq_tok0, seq_slot, n_seqs):
+    """state[slot of s] = inp[last row of sequence s], as float32."""
+    _f32(state, "state")
+    _need(inp.is_contiguous() and inp.dim() == 2 and state.shape[1] == inp.shape[1], "save_last_rows: shapes")
+    _check(lib().edgelm_save_last_rows(_p(inp), _dt(inp), _p(state), _p(seq_tok0), _p(seq_slot), int(n_seqs), inp.shape[1], _stream()))
+
+
+def conv_silu(u, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_seqs):
+    """Causal convolution over the channels u[:, off : off + C] with taps w [C, taps] and bias b, then silu; the inputs
+    before the step come from state [slots, taps - 1, C], which is then moved on to the step's last inputs."""
+    for t, n in ((u, "u"), (w, "w"), (b, "b"), (state, "state"), (out, "out")):
+        _f32(t, n)
+    T, C = out.shape
+    taps = w.shape[1]
+    _need(u.shape[0] == T and w.shape[0] == C and b.numel() == C and tuple(state.shape[1:]) == (taps - 1, C), "conv_silu: shapes")
+    _check(lib().edgelm_conv_silu(_p(u), u.stride(0), int(off), _p(w), _p(b), _p(state), _p(out), _p(tok_seq), _p(seq_tok0), _p(seq_slot),
+                                  T, int(n_seqs), C, taps, _stream()), launches=2 if taps > 1 else 1)
+
+
+def ssm_scan(xbc, u, dt_off, dt_bias, a_log, d, state, y, seq_tok0, seq_slot, n_seqs, heads, groups, n_state, head_dim):
+    """The selective state-space recurrence over the step's tokens.  xbc [T, H P + 2 G N] (x | B | C after the
+    convolution), the raw step sizes at u[:, dt_off + h]; state [slots, H, P, N]; y [T, H P]."""
+    for t, n in ((xbc, "xbc"), (u, "u"), (dt_bias, "dt_bias"), (a_log, "A_log"), (d, "D"), (state, "state"), (y, "y")):
+        _f32(t, n)
+    inner = heads * head_dim
+    _need(xbc.shape[1] == inner + 2 * groups * n_state and y.shape == (xbc.shape[0], inner) and u.shape[0] == xbc.shape[0], "ssm_scan: shapes")
+    _need(tuple(state.shape[1:]) == (heads, head_dim, n_state) and dt_bias.numel() == heads and a_log.numel() == heads and d.numel() == heads, "ssm_scan: state or per-head vectors")
+    _check(lib().edgelm_ssm_scan(_p(xbc), xbc.shape[1], inner, groups, n_state, _p(u), u.stride(0), int(dt_off), _p(dt_bias), _p(a_log),
+                                 _p(d), _p(state), _p(y), _p(seq_tok0), _p(seq_slot), int(n_seqs), heads, head_dim, _stream()))
+
+
+def wkv_scan(r, k, v, w, bonus, state, o, seq_tok0, seq_slot, n_seqs, heads, head_dim):
+    """o_t = (S + diag(bonus) k_t v_t^T)^T r_t, then S <- diag(w_t) S + k_t v_t^T, per head.  r, k, v, w, o: [T, H K]
+    float32; state [slots, H, K (value), K (key)]."""
+    for t, n in ((r, "r"), (k, "k"), (v, "v"), (w, "w"), (bonus, "bonus"), (state, "state"), (o, "o")):
+        _f32(t, n)
+    _need(r.shape == k.shape == v.shape == w.shape == o.shape and r.shape[1] == heads * head_dim, "wkv_scan: shapes")
+    _need(tuple(state.shape[1:]) == (heads, head_dim, head_dim) and bonus.numel() == heads * head_dim, "wkv_scan: state or bonus")
+    _check(lib().edgelm_wkv_scan(_p(r), _p(k), _p(v), _p(w), _p(bonus), _p(state), _p(o), _p(seq_tok0), _p(seq_slot), int(n_seqs),
+                                 heads, head_dim, _stream()))
+
+
+def lowrank_decay(a, w2, w0, out):
+    """out = exp(-exp(w0 + tanh(a) @ w2.T)) in float32; a [T, L] float32, w2 [C, L] float32 or bfloat16."""
+    _f32(a, "a"); _f32(w0, "w0"); _f32(out, "out")
+    T, L = a.shape
+    C = w2.shape[0]
+    _need(w2.is_contiguous() and w2.shape == (C, L) and w0.numel() == C and out.shape == (T, C), "lowrank_decay: shapes")
+    _check(lib().edgelm_lowrank_decay(_p(a), _p(w2), _dt(w2), _p(w0), _p(out), T, C, L, _stream()))
+
+
+def gated_group_norm(y, gate, w, out, groups, eps, gate_first):
+    """RMS norm of y [T, inner] in `groups` equal parts with weight w, gated by silu(gate) before the norm
+    (`gate_first`) or after it.  gate: float32 rows of any stride."""
+    _f32(y, "y"); _f32(w, "w")
+    T, inner = y.shape
+    _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (T, inner) and out.is_contiguous() and out.shape == (T, inner), "gated_group_norm: shapes")
+    _check(lib().edgelm_gated_group_norm(_p(y), _p(gate), gate.stride(0), _p(w), _p(out), _dt(out), T, inner, int(groups),
+                                         ctypes.c_float(eps), 1 if gate_first else 0, _stream()))
+
+
+def rmsnorm_add(x, y1, w, eps, a=1.0, y2=None, b=0.0, cast=None):
+    """x += rmsnorm(a y1 + b y2) * w, all float32; `cast` (optional, [T, D] in the compute dtype) receives the new x too."""
+    _f32(x, "x"); _f32(y1, "y1"); _f32(w, "w")
+    _need(y1.shape == x.shape and (y2 is None or (y2.shape == x.shape and y2.dtype == torch.float32 and y2.is_contiguous())), "rmsnorm_add: shapes")
+    _need(cast is None or (cast.shape == x.shape and cast.is_contiguous()), "rmsnorm_add: the copy's layout")
+    _check(lib().edgelm_rmsnorm_add(_p(x), _p(y1), ctypes.c_float(a), _p(y2), ctypes.c_float(b), _p(w), _p(cast),
+                                    _dt(cast) if cast is not None else F32, x.shape[0], x.shape[1], ctypes.c_float(eps), _stream()))
+
+
+def scaled_sum(y1, a, y2, b, out):
+    """out = a y1 + b y2 (float32, equal shapes)."""
+    _f32(y1, "y1"); _f32(y2, "y2"); _f32(out, "out")
+    _need(y1.shape == y2.shape == out.shape, "scaled_sum: shapes")
+    _check(lib().edgelm_scaled_sum(_p(y1), ctypes.c_float(a), _p(y2), ctypes.c_float(b), _p(out), ctypes.c_longlong(out.numel()), _stream()))
+
+
+def _pooled_cache_check(kcache, vcache, nkv, dk, dv, what):
+    _need(kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == vcache.dtype, f"{what}: cache layout")
+    _need(tuple(kcache.shape[1:]) == (nkv, PAGE, dk) and tuple(vcache.shape[1:]) == (nkv, PAGE, dv) and vcache.shape[0] == kcache.shape[0], f"{what}: cache shape")
+
+
+def qk_rope_norm_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache, nh, nkv, dk, dv, rot, freq, eps, unit_norm, err):
+    """qkv [T, nh dk + nkv dk + nkv dv] float32 (+ bias): rotate the first `rot` dimensions of every query and key
+    head by position * freq (pairs i, i + rot/2), divide each head by its root mean square (`unit_norm`), write the
+    queries to q_out [T, nh dk] and the keys and values to their places in the cache pages."""
+    _f32(qkv, "qkv")
+    T = qkv.shape[0]
+    _need(qkv.shape[1] == (nh + nkv) * dk + nkv * dv and q_out.shape == (T, nh * dk) and q_out.is_contiguous() and q_out.dtype == kcache.dtype, "qk_rope_norm_append: shapes")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == qkv.shape[1]), "qk_rope_norm_append: bias")
+    _need(rot == 0 or (freq is not None and freq.dtype == torch.float32 and freq.numel() == rot // 2 and freq.is_contiguous()), "qk_rope_norm_append: frequencies")
+    _pooled_cache_check(kcache, vcache, nkv, dk, dv, "qk_rope_norm_append")
+    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (page_table, "page_table")):
+        _i32(t, n)
+    _check(lib().edgelm_qk_rope_norm_append(_p(qkv), _p(bias), _p(q_out), _dt(q_out), _p(tok_pos), _p(tok_seq), _p(page_table),
+                                            page_table.stride(0), kcache.shape[0], _p(kcache), _p(vcache), T, nh, nkv, dk, dv, int(rot),
+                                            _p(freq), ctypes.c_float(eps), 1 if unit_norm else 0, _p(err), _stream()))
+
+
+def pool_blocks(tok_pos, tok_seq, page_table, kcache, vcache, pooled_k, pooled_v, n_tokens, nkv, dk, dv, pool, err):
+    """For every token of the step that ends a block of `pool` positions: the block's mean key and value, from the
+    cache pages into the pooled rows."""
+    _pooled_cache_check(kcache, vcache, nkv, dk, dv, "pool_blocks")
+    _f32(pooled_k, "pooled_k"); _f32(pooled_v, "pooled_v")
+    rows = pooled_k.shape[2]
+    _need(tuple(pooled_k.shape) == (kcache.shape[0], nkv, rows, dk) and tuple(pooled_v.shape) == (kcache.shape[0], nkv, rows, dv), "pool_blocks: pooled layout")
+    _check(lib().edgelm_pool_blocks(_p(tok_pos), _p(tok_seq), _p(page_table), page_table.stride(0), kcache.shape[0], _p(kcache), _p(vcache),
+                                    _dt(kcache), _p(pooled_k), _p(pooled_v), int(n_tokens), nkv, dk, dv, int(pool), rows, _p(err), _stream()))
+
+
+def pooled_window_attn(q, out, kcache, vcache, pooled_k, pooled_v, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, window, pool):
+    """Attention of every token of the step over the last `window` keys and one pooled key per block of `pool`
+    positions wholly before the window (`pool` 0 or None: the window alone), one softmax over both."""
+    T = q.shape[0]
+    _need(q.is_contiguous() and out.is_contiguous() and q.shape == (T, nh * dk) and out.shape == (T, nh * dv) and q.dtype == out.dtype == kcache.dtype, "pooled_window_attn: shapes")
+    _pooled_cache_check(kcache, vcache, nkv, dk, dv, "pooled_window_attn")
+    rows = 0
+    if pool:
+        _f32(pooled_k, "pooled_k"); _f32(pooled_v, "pooled_v")
+        rows = pooled_k.shape[2]
+        _need(tuple(pooled_k.shape) == (kcache.shape[0], nkv, rows, dk) and tuple(pooled_v.shape) == (kcache.shape[0], nkv, rows, dv), "pooled_window_attn: pooled layout")
+    _check(lib().edgelm_pooled_window_attn(_p(q), _p(out), _p(kcache), _p(vcache), _dt(q), _p(pooled_k) if pool else _p(None),
+                                           _p(pooled_v) if pool else _p(None), _p(tok_pos), _p(tok_seq), _p(page_table), page_table.stride(0),
+                                           kcache.shape[0], T, nh, nkv, dk, dv, ctypes.c_float(scale), int(window), int(pool or 0), rows, _stream()))

@@ -2,7 +2,8 @@
 about it, packed into one host buffer that goes to the device in one copy.
 
 Tokens of all sequences are packed along one axis.  Per token: its id, its absolute position
-and its sequence's index in the batch.  Per sequence: the position of its last new token, and
+and its sequence's index in the batch.  Per sequence: the position of its last new token, the
+packed row of its first token (one entry more closes the list: the step's token count), and
 its row of each cache group's page table.  For steps with more than one token per sequence
 there are also attention tiles (runs of at most `tile_tokens` consecutive tokens of one
 sequence).  Nothing here is padded: a kernel sees exactly the tokens the step brings.
@@ -57,6 +58,7 @@ class StepContext:
         self.all_single = False
         self.weights_after = ()
         self.token_ids = self.tok_pos = self.tok_seq = self.seq_index = self.seq_pos = self.want_rows = None
+        self.seq_tok0 = None           # packed row of each sequence's first token, then the token count (int32 [n_seqs + 1])
         self.seq_slots = None          # real slot of each sequence (int32 device tensor): state groups, sampler streams
         self._tables = {}              # cache group id -> device page-table rows [n_seqs, stride]
         self._tiles = {}
@@ -122,7 +124,7 @@ class BatchBuffers:
         self.groups = list(kv_groups)
         self.stride = {g.id: g.table.shape[1] for g in self.groups}
         self.tile_sizes = sorted(set(int(t) for t in tile_sizes))
-        n = 3 * max_tokens + 4 * max_seqs + max_want + sum(max_seqs * s for s in self.stride.values())
+        n = 3 * max_tokens + 5 * max_seqs + 1 + max_want + sum(max_seqs * s for s in self.stride.values())
         n += sum(4 * (max_tokens // t + max_seqs) for t in self.tile_sizes)
         self.host = torch.zeros(n, dtype=torch.int32).pin_memory()
         self.host_np = self.host.numpy()
@@ -158,6 +160,7 @@ class BatchBuffers:
         put("tok_pos", (np.arange(T, dtype=np.int64) - np.repeat(starts, ntok) + np.repeat(pos0, ntok)).astype(np.int32), T)
         put("tok_seq", seq_of_tok, T)
         put("seq_pos", (pos0 + ntok - 1).astype(np.int32), B)
+        put("seq_tok0", np.concatenate([starts, [T]]).astype(np.int32), B + 1)
         put("want_rows", np.asarray(want_rows, dtype=np.int32), R)
         slots = np.asarray(seq_slots, dtype=np.int64)
         put("seq_slots", slots.astype(np.int32), B)
@@ -189,6 +192,7 @@ class BatchBuffers:
         ctx.all_single = bool(T == B and T > 0)
         ctx.token_ids, ctx.tok_pos, ctx.tok_seq = view("token_ids"), view("tok_pos"), view("tok_seq")
         ctx.seq_pos, ctx.want_rows = view("seq_pos"), view("want_rows")
+        ctx.seq_tok0 = view("seq_tok0")
         ctx.seq_index = self.seq_index_full[:B]
         ctx._tables = {g.id: view(("table", g.id)).view(B, self.stride[g.id]) for g in self.groups}
         ctx._tiles = {ts: Tiles(view(("tiles", ts, 0)), view(("tiles", ts, 1)), view(("tiles", ts, 2)), view(("tiles", ts, 3)), n)

@@ -49,6 +49,9 @@ def load_model(model_dir, dtype="bfloat16", device="cuda:0"):
     ops.require_device()
     torch_dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
     config = read_config(model_dir)
+    if hasattr(config, "shape_given_sizes"):    # an architecture some of whose sizes only the stored tensors' shapes give
+        from ..weights import read_dir
+        config = config.shape_given_sizes({name: tuple(t.shape) for name, t in read_dir(model_dir).items()})
     model = DecoderModel(config.plan(), torch_dtype)
     tensors = load_checked(model_dir, model.expected_weights(), model.ignorable_weights())
     model.load(tensors, device)

@@ -5,7 +5,9 @@ Every part, whatever its role, answers four questions:
   weight_shapes(prefix) -> {tensor name: shape}   which tensors it wants from the weights file
   load(tensors, prefix, device)                   take them (name -> CPU tensor in the stored dtype)
   workspace_bytes(n_tokens, n_seqs) -> int        scratch it takes from the step's workspace
-  cache_need() -> KVNeed | StateNeed | None       what it keeps per sequence between steps (mixers)
+  cache_need() -> KVNeed | StateNeed | NeedSet | None
+                                                  what it keeps per sequence between steps (mixers, and
+                                                  block arrangements with a state of their own)
 
 two about itself, which the command line and the benchmark add up instead of reading any
 architecture's configuration fields:
@@ -38,16 +40,32 @@ import torch
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values for every position (`window` None) or for the last `window` positions."""
+    """Keys and values for every position (`window` None) or for the last `window` positions.  `v_head_dim`: the
+    size of a value head where it differs from a key head's.  `pool`: beside the pages, one float32 key and value
+    row per block of `pool` consecutive positions (the block's mean, written by the mixer when the block is full),
+    kept in the page that holds the block's last position: `CacheEntry.pooled_k / pooled_v`."""
     n_kv_heads: int
     head_dim: int
     window: int = None
+    v_head_dim: int = None
+    pool: int = None
 
 
 @dataclass(frozen=True)
 class StateNeed:
     """A state of fixed size per sequence: a float32 tensor of this shape, zero when a sequence starts."""
     shape: Tuple[int, ...]
+
+
+@dataclass(frozen=True)
+class NeedSet:
+    """Several things that one layer run keeps per sequence, by name: `(("conv", StateNeed(...)), ("ssm", StateNeed(...)))`.
+    An item may be a NeedSet itself (a mixer made of mixers).  The layer run's cache entry then answers `entry[name]`."""
+    items: Tuple[Tuple[str, object], ...]
+
+    @classmethod
+    def of(cls, **needs):
+        return cls(tuple((k, v) for k, v in needs.items() if v is not None))
 
 
 class Part:

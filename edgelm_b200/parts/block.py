@@ -1,7 +1,12 @@
-"""Arrangement of one layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
-(adarsh-sgh/edgelm tools/elm.py:122-153)."""
+"""Arrangements of one layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
+(adarsh-sgh/edgelm tools/elm.py:122-153).  "sublayer_norm": x += norm1(mixer(x)); x += norm2(ffn(x)), with an
+optional blend of the mixer's input with the previous token's."""
+import torch
+
+from ..config.base import ConfigError
+from ..csrc import ops
 from . import linear
-from .base import Part, nbytes
+from .base import NeedSet, Part, StateNeed, as_vector, nbytes
 from .registry import register_block
 
 
@@ -77,3 +82,104 @@ class PreNormBlock(Part):
         ctx.weights_after = after_layer
         with ctx.ws.frame():
             self.ffn.forward(ctx, self._normed(ctx, x, self.ffn_norm, self.ffn), x)
+
+
+@register_block("sublayer_norm")
+class SublayerNormBlock(Part):
+    """The norm on each sublayer's OUTPUT: x += norm1(mixer(h)); x += norm2(ffn(x)), the sublayers reading the
+    residual stream itself.  With the option `shift` (a tensor's name) the mixer's input is first blended with the
+    previous token's: h_t = x_t + (x_(t-1) - x_t) * shift, element by element, with zeros before a sequence's first
+    token; the last x of every sequence is then part of its state (a float32 row of its own beside the mixer's).
+    A layer may have no feed-forward.  Mixers and feed-forwards are asked to STORE their output (`accumulate=False`):
+    the residual sum is the norm kernel's, which also hands the feed-forward its input in the compute dtype."""
+
+    def __init__(self, layer_spec, env):
+        self.prefix = layer_spec.prefix
+        self.dtype = env.dtype
+        self.mixer_norm = env.build("norm", layer_spec.mixer_norm)
+        self.mixer = env.build("mixer", layer_spec.mixer)
+        self.ffn = env.build("ffn", layer_spec.ffn) if layer_spec.ffn is not None else None
+        self.ffn_norm = env.build("norm", layer_spec.ffn_norm) if layer_spec.ffn is not None else None
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not hasattr(n, "add_normed"):
+                raise ConfigError(f"block 'sublayer_norm': the norm '{n.kind}' cannot be applied to a sublayer's output (no add_normed)")
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
+        self.hidden = layer_spec.mixer_norm["dim"]
+        self.shift_name = layer_spec.options.get("shift")
+        self.shift = None
+
+    def weight_shapes(self, prefix=None):
+        out = {}
+        for p in self.parts:
+            out.update(p.weight_shapes(self.prefix))
+        if self.shift_name:
+            out[self.prefix + self.shift_name] = (self.hidden,)
+        return out
+
+    def load(self, tensors, prefix, device):
+        for p in self.parts:
+            p.load(tensors, self.prefix, device)
+        if self.shift_name:
+            self.shift = as_vector(tensors[self.prefix + self.shift_name], device).view(1, self.hidden)
+
+    def cache_need(self):
+        return NeedSet.of(shift=StateNeed((self.hidden,)) if self.shift_name else None, mixer=self.mixer.cache_need())
+
+    def sizes(self):
+        out = {}
+        for p in (self.mixer, self.ffn, self.mixer_norm):
+            if p is not None:
+                out.update(p.sizes())
+        out["token_shift"] = bool(self.shift_name)
+        return out
+
+    def flops(self, n_tokens, attended):
+        return sum(p.flops(n_tokens, attended) for p in self.parts)
+
+    def describe(self):
+        ffn = f"; x += {self.ffn_norm.describe()}({self.ffn.describe()})" if self.ffn is not None else ""
+        return f"{self.kind}{' with token shift' if self.shift_name else ''}: x += {self.mixer_norm.describe()}({self.mixer.describe()}){ffn}"
+
+    def tile_sizes(self):
+        return tuple(self.mixer.tile_sizes())
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
+    def workspace_bytes(self, n_tokens, n_seqs):
+        inner = max(self.mixer.workspace_bytes(n_tokens, n_seqs), self.ffn.workspace_bytes(n_tokens, n_seqs) if self.ffn is not None else 0)
+        return nbytes((n_tokens, self.hidden), self.dtype) + nbytes((n_tokens, self.hidden), torch.float32) + inner
+
+    def first_weights(self):
+        return self.mixer.first_weights()
+
+    def forward(self, ctx, x, cache):
+        T, ws = x.shape[0], ctx.ws
+        after_layer = ctx.weights_after
+        with ws.frame():
+            h = ws.alloc((T, self.hidden), self.dtype)      # the mixer's input; later the feed-forward's
+            y = ws.alloc((T, self.hidden), torch.float32)   # a sublayer's output before its norm
+            if self.shift is not None:
+                state = cache["shift"].state
+                with ctx.prof("token_shift"):
+                    ops.shift_mix(x, state, self.shift, h.view(1, T, self.hidden), ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots)
+                    ops.save_last_rows(x, state, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs)
+                mixer_in = h
+            elif self.dtype == torch.float32:
+                mixer_in = x
+            else:
+                h.copy_(x)
+                mixer_in = h
+            ctx.weights_after = self.ffn.first_weights() if self.ffn is not None else after_layer
+            with ws.frame():
+                self.mixer.forward(ctx, mixer_in, y, cache.get("mixer"), accumulate=False)
+            ctx.weights_after = after_layer
+            feeds = self.ffn is not None and self.dtype != torch.float32
+            with ctx.prof("norm_residual"):
+                self.mixer_norm.add_normed(ctx, x, y, cast=h if feeds else None)
+            if self.ffn is not None:
+                with ws.frame():
+                    self.ffn.forward(ctx, h if feeds else x, y, accumulate=False)
+                with ctx.prof("norm_residual"):
+                    self.ffn_norm.add_normed(ctx, x, y)

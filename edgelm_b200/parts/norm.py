@@ -25,3 +25,8 @@ class RMSNorm(Part):
 
     def forward(self, ctx, x, out, rows=None):
         ops.rmsnorm(x, self.weight, self.eps, out, rows_idx=rows)
+
+    def add_normed(self, ctx, x, y, cast=None, a=1.0, y2=None, b=0.0):
+        """x += norm(a y + b y2): the norm on a sublayer's OUTPUT, with the residual sum in the same kernel.  x, y, y2
+        float32; `cast` (optional) receives the new x in the compute dtype, for the matrix product that reads it next."""
+        ops.rmsnorm_add(x, y, self.weight, self.eps, a=a, y2=y2, b=b, cast=cast)

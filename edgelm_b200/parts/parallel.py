@@ -1,0 +1,75 @@
+"""Two mixers side by side on the same input: x (+)= left_scale * left(h) + right_scale * right(h).  Each keeps what it
+keeps (the layer run's cache entry answers `entry["left"]` and `entry["right"]`)."""
+import torch
+
+from ..csrc import ops
+from .base import NeedSet, Part, nbytes
+from .registry import register_mixer
+
+
+@register_mixer("parallel")
+class ParallelMixers(Part):
+    def __init__(self, spec, env):
+        self.hidden = spec["hidden_size"]
+        self.left, self.right = env.build("mixer", spec["left"]), env.build("mixer", spec["right"])
+        self.left_scale, self.right_scale = float(spec["left_scale"]), float(spec["right_scale"])
+        self.dtype = env.dtype
+        self.parts = (self.left, self.right)
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
+    def sizes(self):
+        out = {"left_scale": self.left_scale, "right_scale": self.right_scale}
+        for p in self.parts:
+            out.update(p.sizes())
+        return out
+
+    def describe(self):
+        return f"parallel({self.left_scale} * {self.left.describe()} + {self.right_scale} * {self.right.describe()})"
+
+    def flops(self, n_tokens, attended):
+        return sum(p.flops(n_tokens, attended) for p in self.parts)
+
+    def weight_shapes(self, prefix):
+        out = {}
+        for p in self.parts:
+            out.update(p.weight_shapes(prefix))
+        return out
+
+    def load(self, tensors, prefix, device):
+        for p in self.parts:
+            p.load(tensors, prefix, device)
+
+    def first_weights(self):
+        return self.left.first_weights()
+
+    def tile_sizes(self):
+        return tuple(self.left.tile_sizes()) + tuple(self.right.tile_sizes())
+
+    def cache_need(self):
+        return NeedSet.of(left=self.left.cache_need(), right=self.right.cache_need())
+
+    def workspace_bytes(self, n_tokens, n_seqs):
+        return 2 * nbytes((n_tokens, self.hidden), torch.float32) + max(p.workspace_bytes(n_tokens, n_seqs) for p in self.parts)
+
+    def forward(self, ctx, h, x, cache, accumulate=True):
+        from . import linear
+        h = linear.as_tensor(h)
+        T, ws = h.shape[0], ctx.ws
+        y1 = ws.alloc((T, self.hidden), torch.float32)
+        y2 = ws.alloc((T, self.hidden), torch.float32)
+        after = ctx.weights_after
+        ctx.weights_after = self.right.first_weights()
+        with ws.frame():
+            self.left.forward(ctx, h, y1, cache.get("left"), accumulate=False)
+        ctx.weights_after = after
+        with ws.frame():
+            self.right.forward(ctx, h, y2, cache.get("right"), accumulate=False)
+        with ctx.prof("parallel_sum"):
+            if accumulate:
+                ops.scaled_sum(y1, self.left_scale, y2, self.right_scale, y1)
+                x.add_(y1)
+            else:
+                ops.scaled_sum(y1, self.left_scale, y2, self.right_scale, x)

@@ -41,9 +41,12 @@ class SwiGLU(Part):
     def first_weights(self):
         return (self.w_gate, self.w_up)
 
-    def forward(self, ctx, h, x):
+    def forward(self, ctx, h, x, accumulate=True):
+        """x += feed_forward(h); with `accumulate` False, x = feed_forward(h) (float32), for an arrangement that
+        norms the sublayer's output before the residual sum."""
         mid = ctx.ws.alloc((h.shape[0], self.inter), self.dtype)
         with ctx.prof("gate_up_swiglu"):
             linear.matmul(ctx, h, self.w_gate, mid, epilogue=linear.EPI_SWIGLU, w2=self.w_up, prefetch=(self.w_down,))
         with ctx.prof("down_proj_residual"):
-            linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL, residual=x, prefetch=ctx.weights_after)
+            linear.matmul(ctx, mid, self.w_down, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
+                          residual=x if accumulate else None, prefetch=ctx.weights_after)
