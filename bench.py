@@ -3,6 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--preset smollm2-135m] [--batch 8] [--sizes a,b | none]
     python bench.py --impl reference ...
+    python bench.py --design sagizen        # that design beside the Llama decoder at equal sizes (a line of its own shape)
 
 A "step" is one decode step of the whole batch.  The default run has the layer sizes of the
 SmolLM2-135M-shaped configuration with random weights N(0, 0.02), bfloat16, a batch of 8
@@ -258,6 +259,82 @@ def measure(preset, args, peaks, steps, warmup, batches, with_clocks):
     return out
 
 
+DESIGN_PAIRS = {"sagizen": [("sagizen-576", "smollm2-135m", 8), ("sagizen-2048", "smollm2-1.7b", 4)]}
+
+
+def parts_profile(model, vocab, ctx, prompt_tokens=2048, batch=8):
+    """Device time of every part of one prompt step (`prompt_tokens` tokens) and of one decode step of `batch`
+    sequences that hold `prompt_tokens` tokens each, from the engine's own per-part profiler (eager steps)."""
+    import torch
+    from edgelm_b200.engine.engine import Engine, StepEntry
+    engine = Engine(model, max_tokens=batch * ctx, max_step_tokens=8192, profile=True)
+    out = {}
+    for phase, reps in (("prefill", 3), ("decode", 6)):
+        slots = engine.open(batch if phase == "decode" else 1)
+        prompts = [random_prompt(prompt_tokens, vocab, 50 + i) for i in range(len(slots))]
+        if phase == "decode":
+            engine.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+        for r in range(reps):
+            if r == reps - 1:
+                engine.profiler.resolve()
+                engine.profiler.events = []
+            if phase == "prefill":
+                engine.close(slots)
+                slots = engine.open(1)
+                engine.step([StepEntry(slots[0], prompts[0], [prompt_tokens - 1])])
+            else:
+                engine.step([StepEntry(s, [int(p[r])], [0]) for s, p in zip(slots, prompts)])
+        rows = {}
+        for e in engine.profiler.resolve():
+            if e["phase"] != "phase":
+                rows[e["name"]] = rows.get(e["name"], 0.0) + e["dur_us"]
+        out[phase] = {k: round(v, 1) for k, v in sorted(rows.items(), key=lambda kv: -kv[1])}
+        engine.close(slots)
+    engine.check_device_errors()
+    del engine
+    torch.cuda.empty_cache()
+    return out
+
+
+def design_bench(args, peaks):
+    """`--design NAME`: the named design beside the closest earlier model at equal width, feed-forward width, head size,
+    vocabulary and depth, random weights: a prompt of 2,048 tokens (kernels alone, from the captured step), decode
+    steps of `--batch` sequences (device time), and every part's device time in both."""
+    import torch
+    from edgelm_b200.engine.engine import Engine
+    from edgelm_b200.presets import preset_config, random_model
+    from edgelm_b200.sampling import SamplingParams
+    steps, warmup = min(max(1, args.steps), 64), max(3, args.warmup)
+    params = SamplingParams(0.0, 40, 42)
+    result = {"metric": "prefill and decode tok/s of a design beside the closest earlier model", "design": args.design, "dtype": args.dtype,
+              "n_gpus": 1, "steps": steps, "warmup": warmup, "data": "synthetic: random weights N(0,0.02), uniform random token ids",
+              "peaks": dict(peaks), "pairs": []}
+    for new, old, layers in DESIGN_PAIRS[args.design]:
+        pair = {"layers": layers}
+        for tag, preset in (("design", new), ("closest", old)):
+            model = random_model(preset_config(preset), seed=0, sigma=0.02, dtype=args.dtype, layers=layers)
+            vocab = model.plan.vocab_size
+            engine = Engine(model, max_tokens=args.batch * args.ctx, max_step_tokens=8192, use_graphs=not args.no_graphs)
+            dev = time_decode(engine, params, args.batch, steps, warmup, args.ctx, vocab, seed=11, e2e=False)
+            step_ms, kernel_ms = time_prefill(engine, 2048, vocab, seed=5)
+            flops = model.flops(2048, 2048 * 2049 / 2.0, 1)
+            rec = {"preset": preset, "weights_mb": round(model.weight_bytes() / 1e6, 1),
+                   "decode_tok_s": round(dev["tok_s"], 1), "decode_ms_per_step": round(dev["ms"] / dev["steps"], 4), "decode_launches_per_step": dev["launches"] // dev["steps"],
+                   "decode_weights_gb_s": round(model.weight_bytes() / (dev["ms"] / 1e3 / dev["steps"]) / 1e9, 1),
+                   "prefill_tok_s": round(2048 / (step_ms / 1e3), 1), "prefill_ms": round(step_ms, 3),
+                   "prefill_kernels_ms": round(kernel_ms, 3) if kernel_ms else None, "prefill_gflop": round(flops / 1e9, 1),
+                   "prefill_frac": round(flops / ((kernel_ms or step_ms) / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
+            del engine
+            torch.cuda.empty_cache()
+            rec["parts_us"] = parts_profile(model, vocab, args.ctx, batch=args.batch)
+            pair[tag] = rec
+            del model
+            torch.cuda.empty_cache()
+        result["pairs"].append(pair)
+    print(json.dumps(result))
+    return 0
+
+
 def summary(m):
     """The figures of one shape as a small dict (for `sizes`)."""
     d = {"layers": len(m["model"].schedule), "layers_of_preset": m["full_layers"]}
@@ -289,6 +366,8 @@ def main():
     ap.add_argument("--sizes", default="smollm2-360m,smollm2-1.7b", help="other shapes measured on the same line, or 'none'")
     ap.add_argument("--no-points", action="store_true", help="only the headline batch: no batch 1 and 64, no long context, no other sizes")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--design", default=None, choices=sorted(DESIGN_PAIRS),
+                    help="measure this design beside the closest earlier model at equal sizes instead of the default workload")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -304,6 +383,8 @@ def main():
     import torch
 
     peaks = read_peaks()
+    if args.design:
+        return design_bench(args, peaks)
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
     main_m = measure(args.preset, args, peaks, steps, warmup, batches, with_clocks=True)
     model, engine = main_m["model"], main_m["engine"]

@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(PW_WARPS * 32)
 qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, T* __restrict__ q_out,
                            const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq,
                            const int32_t* __restrict__ page_table, int table_stride, int n_pages, T* __restrict__ kcache,
-                           T* __restrict__ vcache, int H, int G, int dk, int dv, int rot, const float* __restrict__ freq,
+                           T* __restrict__ vcache, int H, int G, int dk, int dv, int rot, const double* __restrict__ freq,
                            float eps, int unit_norm, int* __restrict__ err) {
   extern __shared__ float stage[];   // PW_WARPS rows of dk floats
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -44,7 +44,7 @@ qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restric
   const int ld = H * dk + G * dk + G * dv;
   const float* row = qkv + (size_t)t * ld;
   float* sh = stage + warp * dk;
-  const float fpos = (float)pos;
+  const double dpos = (double)pos;
   for (int head = warp; head < H + G; head += PW_WARPS) {   // query heads, then key heads
     const float* src = row + (size_t)head * dk;
     const float* b = bias ? bias + (size_t)head * dk : nullptr;
@@ -60,8 +60,12 @@ qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restric
         x = sh[i];
         if (i < rot) {
           const int f = i < half ? i : i - half;
+          // the angle position * f is formed exactly and brought into [-pi, pi] before it is rounded to float32: at
+          // position 1,000 a float32 product alone is off by up to 3e-5 rad, which is most of a float32 model's error
+          double a = dpos * freq[f];
+          a -= 6.283185307179586477 * rint(a * 0.15915494309189533577);
           float sn, cs;
-          sincosf(fpos * freq[f], &sn, &cs);
+          sincosf((float)a, &sn, &cs);
           x = i < half ? sh[i] * cs - sh[i + half] * sn : sh[i] * cs + sh[i - half] * sn;
         }
       }
@@ -121,6 +125,21 @@ __global__ void pool_blocks_kernel(const int32_t* __restrict__ tok_pos, const in
   }
 }
 
+// q . k with four running sums (shorter chains of roundings, and of dependent instructions).
+template <typename TK>
+__device__ __forceinline__ float dot4(const float* __restrict__ q, const TK* __restrict__ k, int n) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int i = 0;
+  for (; i + 4 <= n; i += 4) {
+    a0 = fmaf(q[i], to_f32(k[i]), a0);
+    a1 = fmaf(q[i + 1], to_f32(k[i + 1]), a1);
+    a2 = fmaf(q[i + 2], to_f32(k[i + 2]), a2);
+    a3 = fmaf(q[i + 3], to_f32(k[i + 3]), a3);
+  }
+  for (; i < n; ++i) a0 = fmaf(q[i], to_f32(k[i]), a0);
+  return (a0 + a1) + (a2 + a3);
+}
+
 // One warp per (token, query head).  Keys are walked 32 at a time, a lane a key: pooled blocks first, then the
 // window's tokens; online softmax in float32; the weighted values are gathered with the lanes over the value's
 // dimensions.  q [tokens][H dk], out [tokens][H dv].
@@ -158,10 +177,7 @@ pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T*
         const int page = table[end / PAGE];
         if (page >= 0 && page < n_pages) {
           const size_t rowi = ((size_t)page * G + g) * R + (e - (PAGE * (end / PAGE)) / P);
-          const float* kr = pk + rowi * dk;
-          float acc = 0.f;
-          for (int i = 0; i < dk; ++i) acc = fmaf(qh[i], kr[i], acc);
-          sc = acc;
+          sc = dot4(qh, pk + rowi * dk, dk);
           voff = (long long)(rowi * dv) | (1ll << 62);
         }
       } else {
@@ -169,10 +185,7 @@ pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T*
         const int page = table[p / PAGE];
         if (page >= 0 && page < n_pages) {
           const size_t rowi = ((size_t)page * G + g) * PAGE + p % PAGE;
-          const T* kr = kcache + rowi * dk;
-          float acc = 0.f;
-          for (int i = 0; i < dk; ++i) acc = fmaf(qh[i], to_f32(kr[i]), acc);
-          sc = acc;
+          sc = dot4(qh, kcache + rowi * dk, dk);
           voff = (long long)(rowi * dv);
         }
       }
@@ -216,7 +229,7 @@ using namespace edgelm;
 extern "C" int edgelm_qk_rope_norm_append(const float* qkv, const float* bias, void* q_out, int dtype, const int32_t* tok_pos,
                                           const int32_t* tok_seq, const int32_t* page_table, int table_stride, int n_pages,
                                           void* kcache, void* vcache, int n_tokens, int H, int G, int dk, int dv, int rot,
-                                          const float* freq, float eps, int unit_norm, int* err, cudaStream_t stream) {
+                                          const double* freq, float eps, int unit_norm, int* err, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && H > 0 && G > 0 && H % G == 0, "qk_rope_norm_append: %d query heads over %d key/value heads", H, G);
   EL_REFUSE(dk >= 1 && dk <= 256 && dv >= 1 && dv <= 256, "qk_rope_norm_append: head sizes %d / %d are not taken (1 to 256)", dk, dv);

@@ -49,6 +49,9 @@ gemm_tile_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, co
       if (EPI == EPI_SWIGLU) Ws2[k][r] = ok ? to_f32(W2[(size_t)(n0 + r) * K + gk]) : 0.f;
     }
     __syncthreads();
+    // a tile's products are summed on their own and then added to the running sums: the rounding error of a long
+    // row of products grows with the number of tiles and the tile's length, not with their product
+    float part[4][4] = {}, part2[4][4] = {};
 #pragma unroll
     for (int k = 0; k < BK; ++k) {
       float a[4], b[4], b2[4];
@@ -64,10 +67,17 @@ gemm_tile_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, co
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
-          if (EPI == EPI_SWIGLU) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+          part[i][j] = fmaf(a[i], b[j], part[i][j]);
+          if (EPI == EPI_SWIGLU) part2[i][j] = fmaf(a[i], b2[j], part2[i][j]);
         }
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[i][j] += part[i][j];
+        if (EPI == EPI_SWIGLU) acc2[i][j] += part2[i][j];
+      }
     __syncthreads();
   }
 #pragma unroll

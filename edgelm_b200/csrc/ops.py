@@ -552,13 +552,13 @@ def _pooled_cache_check(kcache, vcache, nkv, dk, dv, what):
 
 def qk_rope_norm_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache, nh, nkv, dk, dv, rot, freq, eps, unit_norm, err):
     """qkv [T, nh dk + nkv dk + nkv dv] float32 (+ bias): rotate the first `rot` dimensions of every query and key
-    head by position * freq (pairs i, i + rot/2), divide each head by its root mean square (`unit_norm`), write the
+    head by position * freq (float64 frequencies; pairs i, i + rot/2), divide each head by its root mean square (`unit_norm`), write the
     queries to q_out [T, nh dk] and the keys and values to their places in the cache pages."""
     _f32(qkv, "qkv")
     T = qkv.shape[0]
     _need(qkv.shape[1] == (nh + nkv) * dk + nkv * dv and q_out.shape == (T, nh * dk) and q_out.is_contiguous() and q_out.dtype == kcache.dtype, "qk_rope_norm_append: shapes")
     _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == qkv.shape[1]), "qk_rope_norm_append: bias")
-    _need(rot == 0 or (freq is not None and freq.dtype == torch.float32 and freq.numel() == rot // 2 and freq.is_contiguous()), "qk_rope_norm_append: frequencies")
+    _need(rot == 0 or (freq is not None and freq.dtype == torch.float64 and freq.numel() == rot // 2 and freq.is_contiguous()), "qk_rope_norm_append: frequencies")
     _pooled_cache_check(kcache, vcache, nkv, dk, dv, "qk_rope_norm_append")
     for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (page_table, "page_table")):
         _i32(t, n)

@@ -71,10 +71,11 @@ class PooledWindowAttention(Part):
         if self.bias:
             self.b_qkv = torch.cat([as_vector(tensors[prefix + n[k] + n["bias"]], device) for k in ("q", "k", "v")]).contiguous()
         if self.rot:
-            # frequencies in float64 on the host, rounded once; the angle position * f_i and its sine and cosine are float32 in the kernel
+            # frequencies in float64; the kernel forms position * f_i exactly, reduces it to [-pi, pi] and takes the float32
+            # sine and cosine of that
             i = torch.arange(self.rot // 2, dtype=torch.float64)
             f = torch.pow(torch.tensor(self.base, dtype=torch.float64), -2.0 * i / self.rot) / self.scaling
-            self.freq = f.to(torch.float32).to(device).contiguous()
+            self.freq = f.to(device).contiguous()
 
     def first_weights(self):
         return (self.w_qkv,)

@@ -9,7 +9,24 @@ def _llama(vocab, hidden, inter, layers, heads, kv_heads, head_dim, max_pos, the
             "rope_theta": theta, "rms_norm_eps": eps, "tie_word_embeddings": tied, "bos_token_id": 0, "eos_token_id": 0}
 
 
+def _sagizen(vocab, width, ff, groups_of_layers, ssm_heads, ssm_state, heads, kv_heads, window, pool):
+    """A Sagizen-shaped model: per group three state-space layers and one layer of attention beside a time mix, heads of
+    64 everywhere, the state-space mixer twice as wide inside as the model (the usual expansion)."""
+    dense = {"kind": "dense", "ff": ff}
+    ssm = {"type": "mamba2", "mlp": dense,
+           "mixer": {"heads": ssm_heads, "vdim": 64, "state": ssm_state, "groups": 1, "conv": 4, "norm_groups": 1}}
+    par = {"type": "parallel", "mlp": dense, "mixer": {
+        "left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "mask": {"size": window, "pool": pool},
+                 "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 1.0}}, "scale": 0.125},
+        "left_scale": 1.0, "right": {"heads": heads, "dim": 64}, "right_scale": 1.0}}
+    return {"architecture": "Sagizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "max_positions": 8192,
+            "layers": [ssm, ssm, ssm, par] * groups_of_layers}
+
+
 PRESETS = {
+    # the layer sizes of smollm2-135m and smollm2-1.7b (width, feed-forward, heads of 64, vocabulary) in the Sagizen design
+    "sagizen-576": _sagizen(49152, 576, 1536, 2, 18, 128, 9, 3, 512, 64),
+    "sagizen-2048": _sagizen(49152, 2048, 8192, 1, 64, 128, 32, 32, 1024, 64),
     "tiny-a": _llama(256, 64, 128, 2, 4, 2, 16, 128, 10000.0, 1e-5, True),
     "tiny-b": _llama(397, 96, 200, 3, 3, 1, 32, 256, 100000.0, 1e-6, False),
     "smollm2-135m": _llama(49152, 576, 1536, 30, 9, 3, 64, 8192, 100000.0, 1e-5, True),
