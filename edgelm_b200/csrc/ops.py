@@ -455,9 +455,10 @@ def _f32(t, name):
     _need(t.dtype == torch.float32 and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous float32 CUDA tensor")
 
 
-def shift_mix(inp, state, mu, out, tok_seq, seq_tok0, seq_slot):
+def shift_mix(inp, state, mu, out, tok_seq, seq_tok0, seq_slot, move_state=False):
     """out[m, t] = a + (prev - a) * mu[m] with a = inp[t] and prev the row before it, or the sequence's state row for
-    the first token that the sequence brings to this step.  inp [T, D] float32 or bfloat16; mu [M, D]; out [M, T, D]."""
+    the first token that the sequence brings to this step.  inp [T, D] float32 or bfloat16; mu [M, D]; out [M, T, D].
+    With `move_state` the state rows then receive each sequence's last row of this step (what `save_last_rows` does)."""
     T, D = inp.shape
     M = mu.shape[0]
     _f32(state, "state"); _f32(mu, "mu")
@@ -465,7 +466,7 @@ def shift_mix(inp, state, mu, out, tok_seq, seq_tok0, seq_slot):
     for t, n in ((tok_seq, "tok_seq"), (seq_tok0, "seq_tok0"), (seq_slot, "seq_slot")):
         _i32(t, n)
     _check(lib().edgelm_shift_mix(_p(inp), _dt(inp), _p(state), _p(mu), _p(out), _dt(out), _p(tok_seq), _p(seq_tok0), _p(seq_slot),
-                                  T, D, M, _stream()))
+                                  T, D, M, 1 if move_state else 0, _stream()))
 
 
 def save_last_rows(inp, state, seq_tok0, seq_slot, n_seqs):
@@ -475,28 +476,41 @@ def save_last_rows(inp, state, seq_tok0, seq_slot, n_seqs):
     _check(lib().edgelm_save_last_rows(_p(inp), _dt(inp), _p(state), _p(seq_tok0), _p(seq_slot), int(n_seqs), inp.shape[1], _stream()))
 
 
-def conv_silu(u, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_seqs):
+def conv_silu(u, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, n_seqs, update_state=True):
     """Causal convolution over the channels u[:, off : off + C] with taps w [C, taps] and bias b, then silu; the inputs
-    before the step come from state [slots, taps - 1, C], which is then moved on to the step's last inputs."""
+    before the step come from state [slots, taps - 1, C], which is then moved on to the step's last inputs (with
+    `update_state` False that is left to the caller: `ssm_scan` does it when it is handed the state)."""
     for t, n in ((u, "u"), (w, "w"), (b, "b"), (state, "state"), (out, "out")):
         _f32(t, n)
     T, C = out.shape
     taps = w.shape[1]
     _need(u.shape[0] == T and w.shape[0] == C and b.numel() == C and tuple(state.shape[1:]) == (taps - 1, C), "conv_silu: shapes")
     _check(lib().edgelm_conv_silu(_p(u), u.stride(0), int(off), _p(w), _p(b), _p(state), _p(out), _p(tok_seq), _p(seq_tok0), _p(seq_slot),
-                                  T, int(n_seqs), C, taps, _stream()), launches=2 if taps > 1 else 1)
+                                  T, int(n_seqs), C, taps, 1 if update_state else 0, _stream()), launches=2 if taps > 1 and update_state else 1)
 
 
-def ssm_scan(xbc, u, dt_off, dt_bias, a_log, d, state, y, seq_tok0, seq_slot, n_seqs, heads, groups, n_state, head_dim):
+def ssm_scan(xbc, u, dt_off, dt_bias, a_log, d, state, y, seq_tok0, seq_slot, n_seqs, heads, groups, n_state, head_dim,
+             conv_state=None, conv_off=0, scratch=None):
     """The selective state-space recurrence over the step's tokens.  xbc [T, H P + 2 G N] (x | B | C after the
-    convolution), the raw step sizes at u[:, dt_off + h]; state [slots, H, P, N]; y [T, H P]."""
+    convolution), the raw step sizes at u[:, dt_off + h]; state [slots, H, P, N]; y [T, H P].  `conv_state`: the tail
+    [slots, taps - 1, channels] of the convolution that made xbc from u[:, conv_off:]; the kernel moves it on.
+    `scratch`: float32 room for 2 T H values (the step sizes and decays, computed once per token and head by a launch
+    of its own); taken from torch when not given."""
     for t, n in ((xbc, "xbc"), (u, "u"), (dt_bias, "dt_bias"), (a_log, "A_log"), (d, "D"), (state, "state"), (y, "y")):
         _f32(t, n)
     inner = heads * head_dim
     _need(xbc.shape[1] == inner + 2 * groups * n_state and y.shape == (xbc.shape[0], inner) and u.shape[0] == xbc.shape[0], "ssm_scan: shapes")
     _need(tuple(state.shape[1:]) == (heads, head_dim, n_state) and dt_bias.numel() == heads and a_log.numel() == heads and d.numel() == heads, "ssm_scan: state or per-head vectors")
+    if conv_state is not None:
+        _f32(conv_state, "conv_state")
+        _need(conv_state.dim() == 3 and conv_state.shape[2] == xbc.shape[1] and conv_off + xbc.shape[1] <= u.shape[1], "ssm_scan: the convolution's tail")
+    T = xbc.shape[0]
+    if scratch is None:
+        scratch = torch.empty(2 * T * heads, dtype=torch.float32, device=xbc.device)
+    _need(scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= 2 * T * heads, "ssm_scan: scratch too small")
     _check(lib().edgelm_ssm_scan(_p(xbc), xbc.shape[1], inner, groups, n_state, _p(u), u.stride(0), int(dt_off), _p(dt_bias), _p(a_log),
-                                 _p(d), _p(state), _p(y), _p(seq_tok0), _p(seq_slot), int(n_seqs), heads, head_dim, _stream()))
+                                 _p(d), _p(state), _p(y), _p(seq_tok0), _p(seq_slot), int(n_seqs), heads, head_dim, _p(conv_state), int(conv_off),
+                                 (conv_state.shape[1] + 1) if conv_state is not None else 1, _p(scratch), T, _stream()), launches=2)
 
 
 def wkv_scan(r, k, v, w, bonus, state, o, seq_tok0, seq_slot, n_seqs, heads, head_dim):

@@ -17,21 +17,25 @@ __device__ __forceinline__ float softplus_exact(float z) { return log1pf(expf(-f
 
 // ------------------------------------------------------------------ blend with the previous token
 // out[m][t][:] = a + (prev - a) * mu[m][:], a = in[t], prev = in[t - 1], or the state row for the first token
-// that a sequence brings to this step (zeros at a sequence's start).
+// that a sequence brings to this step (zeros at a sequence's start).  With `move_state` the block of that first token,
+// the only one that reads the sequence's state row, then writes the sequence's last row of this step into it (each
+// thread the elements it has just read), so that the state needs no kernel of its own.
 template <typename TIn, typename TOut>
-__global__ void shift_mix_kernel(const TIn* __restrict__ in, const float* __restrict__ state, const float* __restrict__ mu,
+__global__ void shift_mix_kernel(const TIn* __restrict__ in, const float* state, const float* __restrict__ mu,
                                  TOut* __restrict__ out, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_tok0,
-                                 const int32_t* __restrict__ seq_slot, int n_tokens, int dim, int n_mix) {
+                                 const int32_t* __restrict__ seq_slot, int n_tokens, int dim, int n_mix, int move_state) {
   const int t = blockIdx.x;
   const int s = tok_seq[t];
   const bool first = t == seq_tok0[s];
-  const float* st = state + (size_t)seq_slot[s] * dim;
+  float* st = const_cast<float*>(state) + (size_t)seq_slot[s] * dim;
   const TIn* cur = in + (size_t)t * dim;
+  const TIn* last = in + (size_t)(seq_tok0[s + 1] - 1) * dim;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
     const float a = to_f32(cur[i]);
     const float p = first ? st[i] : to_f32(cur[i - dim]);
     const float d = p - a;
     for (int m = 0; m < n_mix; ++m) out[((size_t)m * n_tokens + t) * dim + i] = from_f32<TOut>(a + d * mu[(size_t)m * dim + i]);
+    if (first && move_state) st[i] = to_f32(last[i]);
   }
 }
 
@@ -83,72 +87,204 @@ __global__ void conv_state_update_kernel(const float* __restrict__ u, int ldu, i
     }
 }
 
+// Sums over the warp of U values a lane at once: at each of the first log2(U) steps a lane keeps one half of its values
+// and hands the other half to its partner, so U values cost U - 1 + log2(32 / U) shuffles instead of 5 U.  Afterwards the
+// sum of value i is held by the lanes [i * 32 / U, (i + 1) * 32 / U).
+template <int U>
+__device__ __forceinline__ float warp_sums(float (&acc)[U], int lane) {
+  int off = 16;
+#pragma unroll
+  for (int n = U; n > 1; n >>= 1) {
+    const int half = n >> 1;
+    const bool hi = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float keep = hi ? acc[i + half] : acc[i], send = hi ? acc[i] : acc[i + half];
+      acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+    off >>= 1;
+  }
+  float v = acc[0];
+  for (; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+// dt = softplus(raw + bias) and the decay exp(-exp(A_log) dt) of every (token, head), once for all the warps of a head:
+// dta[t][h] = dt, dta[t][H + h] = decay.
+__global__ void ssm_steps_kernel(const float* __restrict__ u, int ldu, int dt_off, const float* __restrict__ dt_bias,
+                                 const float* __restrict__ A_log, float* __restrict__ dta, int n_tokens, int H) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_tokens * H) return;
+  const int t = i / H, h = i - t * H;
+  const float dt = softplus_exact(u[(size_t)t * ldu + dt_off + h] + dt_bias[h]);
+  dta[(size_t)t * 2 * H + h] = dt;
+  dta[(size_t)t * 2 * H + H + h] = expf(-expf(A_log[h]) * dt);
+}
+
 // ------------------------------------------------------------------ selective state-space recurrence
 // Per head h (group g = h / (H / G)) and token t, with dt = softplus(dt_raw + dt_bias[h]) and a = exp(-exp(A_log[h]) dt):
 //   S <- a S + dt B_t x_t^T      (S is N x P)
 //   y_t = S^T C_t + D[h] x_t
-// A warp owns one column p of one head of one sequence; lane l holds the rows n = l, l + 32, ... (NK of them) in
-// registers, so a token costs a handful of multiply-adds and one warp sum, and nothing is exchanged between warps.
-// Tokens are taken U at a time: their inputs are requested together, the warp sums are done together.
+// A warp owns one column p of one head of one sequence; lane l holds the rows n = l NK .. l NK + NK - 1 in registers, so
+// a token costs a handful of multiply-adds and a share of a warp sum, and nothing is exchanged between warps.  The step
+// sizes and decays come from `ssm_steps_kernel`.
+// (The outer-product recurrence further down takes its tokens U at a time through registers: their inputs are requested
+// together, one set ahead of the set that is being computed, and the warp sums of a set are done together.)
 constexpr int SCAN_WARPS = 8;
 
-template <int NK, int U>
+__device__ __forceinline__ void cp_async_4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N_LEFT> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N_LEFT) : "memory"); }
+
+constexpr int SCAN_CHUNK = 8;     // tokens a stage of the ring holds
+constexpr int SCAN_MAX_STAGES = 4;
+
+// The block's eight warps (eight columns p of one head) need the same B_t, C_t, step size and decay, and one x each:
+// all threads bring SCAN_CHUNK tokens' worth of these into a ring in shared memory with asynchronous copies, `stages`
+// - 1 chunks ahead of the chunk that is being computed, so that a token's inputs are on the chip long before its turn
+// and are fetched once a block, not once a warp.  A token's slot: B [NP], C [NP], x [SCAN_WARPS], dt, decay, (pad).
+template <int NK, bool EXACT>     // EXACT: N == 32 NK, every lane's rows exist
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
-ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int G, int N, const float* __restrict__ u, int ldu, int dt_off,
-                const float* __restrict__ dt_bias, const float* __restrict__ A_log, const float* __restrict__ Dp,
+ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int G, int N, const float* __restrict__ u, int ldu,
+                const float* __restrict__ dta, const float* __restrict__ Dp,
                 float* __restrict__ state, float* __restrict__ y, const int32_t* __restrict__ seq_tok0,
-                const int32_t* __restrict__ seq_slot, int H, int P) {
+                const int32_t* __restrict__ seq_slot, int H, int P, float* __restrict__ conv_state, int conv_off, int taps, int vec,
+                int stages) {
+  extern __shared__ __align__(16) float ring[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int s = blockIdx.x / H, h = blockIdx.x - s * H;
-  const int p = blockIdx.y * SCAN_WARPS + warp;
-  if (p >= P) return;
+  if (conv_state != nullptr && taps > 1 && h == 0 && blockIdx.y == 0) {
+    // the convolution that fed this kernel has read its tail; one block a sequence moves the tail on to the step's last
+    // inputs (a thread a channel, rows upwards: a row still to be read lies further on than the row being written)
+    const int c0 = seq_tok0[s], n = seq_tok0[s + 1] - c0;
+    float* cs = conv_state + (size_t)seq_slot[s] * (taps - 1) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+      for (int j = 0; j < taps - 1; ++j) {
+        const int r = n - (taps - 1) + j;
+        cs[(size_t)j * C + c] = r >= 0 ? u[(size_t)(c0 + r) * ldu + conv_off + c] : cs[(size_t)(j + n) * C + c];
+      }
+  }
+  const int p0 = blockIdx.y * SCAN_WARPS, p = p0 + warp;
+  const bool active = p < P;
   const int g = h / (H / G);
   const int t0 = seq_tok0[s], t1 = seq_tok0[s + 1];
-  float* sp = state + (((size_t)seq_slot[s] * H + h) * P + p) * N;
+  const int NP = (N + 3) & ~3, slot = 2 * NP + SCAN_WARPS + 4;
+  const int n0 = lane * NK;            // this lane's rows: n0 .. n0 + NK - 1
+  float* sp = state + (((size_t)seq_slot[s] * H + h) * P + (active ? p : 0)) * N;
   float S[NK];
 #pragma unroll
-  for (int k = 0; k < NK; ++k) S[k] = lane + 32 * k < N ? sp[lane + 32 * k] : 0.f;
-  const float A = -expf(A_log[h]), Dh = Dp[h], bias = dt_bias[h];
-  const int xo = h * P + p, bo = inner + g * N, co = inner + G * N + g * N;
-  for (int tb = t0; tb < t1; tb += U) {
-    float dtr[U], xv[U], Bn[U][NK], Cn[U][NK], acc[U];
-#pragma unroll
-    for (int i = 0; i < U; ++i) {
-      const int t = min(tb + i, t1 - 1);
-      const float* row = xbc + (size_t)t * C;
-      dtr[i] = u[(size_t)t * ldu + dt_off + h];
-      xv[i] = row[xo];
-#pragma unroll
-      for (int k = 0; k < NK; ++k) {
-        const int n = lane + 32 * k;
-        Bn[i][k] = n < N ? row[bo + n] : 0.f;
-        Cn[i][k] = n < N ? row[co + n] : 0.f;
+  for (int k = 0; k < NK; ++k) S[k] = active && n0 + k < N ? sp[n0 + k] : 0.f;
+  const float Dh = Dp[h];
+  const int xo = h * P + p0, bo = inner + g * N, co = inner + G * N + g * N;
+  const int n_chunks = (t1 - t0 + SCAN_CHUNK - 1) / SCAN_CHUNK;
+
+  // which copies this thread makes in every chunk: worked out once (no division inside the loop)
+  const int per_tok = vec ? 2 * (NP >> 2) : 2 * N;           // copies of B and C a token
+  const int step_i = blockDim.x / per_tok, step_r = blockDim.x - step_i * per_tok;
+  const int first_i = threadIdx.x / per_tok, first_r = threadIdx.x - first_i * per_tok;
+  const int small_i = threadIdx.x / (SCAN_WARPS + 2), small_r = threadIdx.x - small_i * (SCAN_WARPS + 2);   // x, dt, decay
+  const float* small_src = small_r < SCAN_WARPS ? xbc + xo + min(small_r, P - 1 - p0) : dta + (size_t)(small_r - SCAN_WARPS) * H + h;
+  const size_t small_ld = small_r < SCAN_WARPS ? (size_t)C : (size_t)2 * H;
+  auto issue = [&](int chunk, int stage) {   // the copies of one chunk into its stage (tokens past the end repeat the last one)
+    if (chunk < n_chunks) {
+      float* base = ring + (size_t)stage * SCAN_CHUNK * slot;
+      const int tc = t0 + chunk * SCAN_CHUNK;
+      for (int i = first_i, r = first_r; i < SCAN_CHUNK;) {
+        const float* row = xbc + (size_t)min(tc + i, t1 - 1) * C;
+        float* dst = base + (size_t)i * slot;
+        if (vec) {
+          const int half = NP >> 2, which = r >= half, q = (r - (which ? half : 0)) << 2;
+          cp_async_16(dst + (which ? NP : 0) + q, row + (which ? co : bo) + q);
+        } else {
+          const int which = r >= N, q = r - (which ? N : 0);
+          cp_async_4(dst + (which ? NP : 0) + q, row + (which ? co : bo) + q);
+        }
+        i += step_i;
+        r += step_r;
+        if (r >= per_tok) { r -= per_tok; ++i; }
       }
+      if (small_i < SCAN_CHUNK)
+        cp_async_4(base + (size_t)small_i * slot + 2 * NP + small_r, small_src + (size_t)min(tc + small_i, t1 - 1) * small_ld);
     }
+    cp_async_commit();                 // (an empty group keeps the count of groups in step with the chunks)
+  };
+
+  for (int c = 0; c < stages - 1; ++c) issue(c, c);
+  int stage = 0;                       // the stage of the chunk being computed; the one before it is refilled
+  for (int chunk = 0; chunk < n_chunks; ++chunk) {
+    // all but the newest stages - 2 groups are complete: chunk `chunk` has landed
+    if (stages == 4) cp_async_wait<2>(); else if (stages == 3) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();                   // everybody's copies of this chunk are visible; everybody is done with chunk - 1
+    issue(chunk + stages - 1, stage == 0 ? stages - 1 : stage - 1);         // into the stage that chunk - 1 used
+    const float* base = ring + (size_t)stage * SCAN_CHUNK * slot;
+    stage = stage + 1 == stages ? 0 : stage + 1;
+    const int tb = t0 + chunk * SCAN_CHUNK;
+    float acc[SCAN_CHUNK], xs[SCAN_CHUNK];
+    auto token = [&](int i, const float* tok) {
+      const float a = tok[2 * NP + SCAN_WARPS + 1], dx = tok[2 * NP + SCAN_WARPS] * xs[i];
+      float Bn[NK], Cn[NK];
+      if (NK >= 4) {
 #pragma unroll
-    for (int i = 0; i < U; ++i) {
-      acc[i] = 0.f;
-      if (tb + i < t1) {
-        const float dt = softplus_exact(dtr[i] + bias);
-        const float a = expf(A * dt), dx = dt * xv[i];
+        for (int k = 0; k < NK; k += 4) {
+          const bool in = EXACT || n0 + k < N;
+          const float4 b4 = in ? *reinterpret_cast<const float4*>(tok + n0 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 c4 = in ? *reinterpret_cast<const float4*>(tok + NP + n0 + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+          Bn[k] = b4.x; Bn[k + 1] = b4.y; Bn[k + 2] = b4.z; Bn[k + 3] = b4.w;
+          Cn[k] = c4.x; Cn[k + 1] = c4.y; Cn[k + 2] = c4.z; Cn[k + 3] = c4.w;
+        }
+      } else if (NK == 2 && EXACT) {
+        const float2 b2 = *reinterpret_cast<const float2*>(tok + n0), c2 = *reinterpret_cast<const float2*>(tok + NP + n0);
+        Bn[0] = b2.x; Bn[1] = b2.y; Cn[0] = c2.x; Cn[1] = c2.y;
+      } else {
 #pragma unroll
         for (int k = 0; k < NK; ++k) {
-          S[k] = fmaf(a, S[k], dx * Bn[i][k]);
-          acc[i] = fmaf(S[k], Cn[i][k], acc[i]);
+          Bn[k] = EXACT || n0 + k < N ? tok[n0 + k] : 0.f;
+          Cn[k] = EXACT || n0 + k < N ? tok[NP + n0 + k] : 0.f;
         }
       }
+#pragma unroll
+      for (int k = 0; k < NK; ++k) {
+        const bool in = EXACT || n0 + k < N;    // (a vector piece may reach past N into the slot's padding)
+        S[k] = in ? fmaf(a, S[k], dx * Bn[k]) : 0.f;
+        acc[i] = in ? fmaf(S[k], Cn[k], acc[i]) : acc[i];
+      }
+    };
+    const float* tok = base;
+    if (tb + SCAN_CHUNK <= t1) {       // a whole chunk: no token needs a check
+#pragma unroll
+      for (int i = 0; i < SCAN_CHUNK; ++i, tok += slot) {
+        acc[i] = 0.f;
+        xs[i] = tok[2 * NP + warp];
+        token(i, tok);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < SCAN_CHUNK; ++i, tok += slot) {
+        acc[i] = 0.f;
+        xs[i] = tok[2 * NP + warp];
+        if (tb + i < t1) token(i, tok);
+      }
     }
+    const float sum = warp_sums<SCAN_CHUNK>(acc, lane);
+    const int i = lane / (32 / SCAN_CHUNK);
+    if (active && (lane & (32 / SCAN_CHUNK - 1)) == 0 && tb + i < t1) {
+      float xi = xs[0];
 #pragma unroll
-    for (int i = 0; i < U; ++i) acc[i] = warp_sum(acc[i]);
-    if (lane == 0) {
-#pragma unroll
-      for (int i = 0; i < U; ++i)
-        if (tb + i < t1) y[(size_t)(tb + i) * inner + xo] = acc[i] + Dh * xv[i];
+      for (int q = 1; q < SCAN_CHUNK; ++q) xi = i == q ? xs[q] : xi;
+      y[(size_t)(tb + i) * inner + xo + warp] = sum + Dh * xi;
     }
   }
+  cp_async_wait<0>();
+  if (active) {
 #pragma unroll
-  for (int k = 0; k < NK; ++k)
-    if (lane + 32 * k < N) sp[lane + 32 * k] = S[k];
+    for (int k = 0; k < NK; ++k)
+      if (n0 + k < N) sp[n0 + k] = S[k];
+  }
 }
 
 // ------------------------------------------------------------------ decayed outer-product recurrence with a bonus
@@ -176,38 +312,47 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ kk, const
     bn[k] = i < K ? bonus[h * K + i] : 0.f;
   }
   const int ld = H * K, ho = h * K;
-  for (int tb = t0; tb < t1; tb += U) {
-    float vj[U], rr[U][NK], kv[U][NK], ww[U][NK], acc[U];
+  struct Inputs { float vj[U], rr[U][NK], kv[U][NK], ww[U][NK]; };
+  auto load = [&](int tb, Inputs& in) {
 #pragma unroll
     for (int q = 0; q < U; ++q) {
       const size_t row = (size_t)min(tb + q, t1 - 1) * ld + ho;
-      vj[q] = v[row + j];
+      in.vj[q] = v[row + j];
 #pragma unroll
       for (int k = 0; k < NK; ++k) {
         const int i = lane + 32 * k;
-        rr[q][k] = i < K ? r[row + i] : 0.f;
-        kv[q][k] = i < K ? kk[row + i] : 0.f;
-        ww[q][k] = i < K ? w[row + i] : 0.f;
+        in.rr[q][k] = i < K ? r[row + i] : 0.f;
+        in.kv[q][k] = i < K ? kk[row + i] : 0.f;
+        in.ww[q][k] = i < K ? w[row + i] : 0.f;
       }
     }
+  };
+  auto compute = [&](int tb, const Inputs& in) {
+    float acc[U];
 #pragma unroll
     for (int q = 0; q < U; ++q) {
       acc[q] = 0.f;
       if (tb + q < t1) {
 #pragma unroll
         for (int k = 0; k < NK; ++k) {
-          const float x = kv[q][k] * vj[q];
-          acc[q] = fmaf(fmaf(bn[k], x, S[k]), rr[q][k], acc[q]);
-          S[k] = fmaf(ww[q][k], S[k], x);
+          const float x = in.kv[q][k] * in.vj[q];
+          acc[q] = fmaf(fmaf(bn[k], x, S[k]), in.rr[q][k], acc[q]);
+          S[k] = fmaf(in.ww[q][k], S[k], x);
         }
       }
     }
-#pragma unroll
-    for (int q = 0; q < U; ++q) acc[q] = warp_sum(acc[q]);
-    if (lane == 0) {
-#pragma unroll
-      for (int q = 0; q < U; ++q)
-        if (tb + q < t1) o[(size_t)(tb + q) * ld + ho + j] = acc[q];
+    const float sum = warp_sums<U>(acc, lane);
+    const int q = lane / (32 / U);
+    if ((lane & (32 / U - 1)) == 0 && tb + q < t1) o[(size_t)(tb + q) * ld + ho + j] = sum;
+  };
+  Inputs ia, ib;
+  if (t0 < t1) load(t0, ia);
+  for (int tb = t0; tb < t1; tb += 2 * U) {
+    if (tb + U < t1) load(tb + U, ib);
+    compute(tb, ia);
+    if (tb + U < t1) {
+      if (tb + 2 * U < t1) load(tb + 2 * U, ia);
+      compute(tb + U, ib);
     }
   }
 #pragma unroll
@@ -303,13 +448,13 @@ extern "C" int edgelm_scaled_sum(const float* y1, float a, const float* y2, floa
 
 static inline int row_threads(int dim) { return dim >= 1024 ? 256 : 128; }
 
-extern "C" int edgelm_shift_mix(const void* in, int in_dtype, const float* state, const float* mu, void* out, int out_dtype,
+extern "C" int edgelm_shift_mix(const void* in, int in_dtype, float* state, const float* mu, void* out, int out_dtype,
                                 const int32_t* tok_seq, const int32_t* seq_tok0, const int32_t* seq_slot, int n_tokens, int dim,
-                                int n_mix, cudaStream_t stream) {
+                                int n_mix, int move_state, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && dim > 0 && n_mix > 0, "shift_mix: bad sizes tokens=%d dim=%d mixes=%d", n_tokens, dim, n_mix);
   const dim3 grid(n_tokens), block(row_threads(dim));
-#define EL_SM(TI, TO) shift_mix_kernel<TI, TO><<<grid, block, 0, stream>>>((const TI*)in, state, mu, (TO*)out, tok_seq, seq_tok0, seq_slot, n_tokens, dim, n_mix)
+#define EL_SM(TI, TO) shift_mix_kernel<TI, TO><<<grid, block, 0, stream>>>((const TI*)in, state, mu, (TO*)out, tok_seq, seq_tok0, seq_slot, n_tokens, dim, n_mix, move_state)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) EL_SM(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) EL_SM(float, __nv_bfloat16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) EL_SM(__nv_bfloat16, __nv_bfloat16);
@@ -330,34 +475,49 @@ extern "C" int edgelm_save_last_rows(const void* in, int in_dtype, float* state,
   return 0;
 }
 
-// The convolution over the step's tokens and, after it, the state for the next step (two launches).
+// The convolution over the step's tokens and, with `update_state`, the state for the next step after it (a second launch).
 extern "C" int edgelm_conv_silu(const float* u, int ldu, int off, const float* w, const float* b, float* state, float* out,
                                 const int32_t* tok_seq, const int32_t* seq_tok0, const int32_t* seq_slot, int n_tokens, int n_seqs,
-                                int C, int taps, cudaStream_t stream) {
+                                int C, int taps, int update_state, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && n_seqs > 0 && C > 0 && taps >= 1 && off >= 0 && off + C <= ldu, "conv_silu: bad sizes C=%d taps=%d", C, taps);
   conv_silu_kernel<<<n_tokens, row_threads(C), 0, stream>>>(u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps);
   EL_LAUNCH_CHECK("conv_silu");
-  if (taps > 1) {
+  if (taps > 1 && update_state) {
     conv_state_update_kernel<<<dim3(n_seqs, (C + 255) / 256), 256, 0, stream>>>(u, ldu, off, state, seq_tok0, seq_slot, C, taps);
     EL_LAUNCH_CHECK("conv_state_update");
   }
   return 0;
 }
 
+// `conv_state` (may be null): the tail [slot][taps - 1][C] of the convolution whose inputs lie at u[:, conv_off + c];
+// the kernel then moves it on to the step's last inputs (`edgelm_conv_silu` with `update_state` 0 left that to it).
+// `dta`: scratch of 2 * n_tokens * H floats for the step sizes and decays (a launch of its own fills it).
 extern "C" int edgelm_ssm_scan(const float* xbc, int C, int inner, int G, int N, const float* u, int ldu, int dt_off,
                                const float* dt_bias, const float* A_log, const float* Dp, float* state, float* y,
-                               const int32_t* seq_tok0, const int32_t* seq_slot, int n_seqs, int H, int P, cudaStream_t stream) {
+                               const int32_t* seq_tok0, const int32_t* seq_slot, int n_seqs, int H, int P, float* conv_state,
+                               int conv_off, int taps, float* dta, int n_tokens, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   EL_REFUSE(n_seqs > 0 && H > 0 && P > 0 && G > 0 && H % G == 0 && inner == H * P && C == inner + 2 * G * N,
             "ssm_scan: sizes do not fit (heads %d, groups %d, head size %d, inner %d, channels %d)", H, G, P, inner, C);
   EL_REFUSE(N >= 1 && N <= 256, "ssm_scan: a state of %d rows per head is not taken (1 to 256)", N);
+  EL_REFUSE(dta != nullptr && n_tokens > 0, "ssm_scan: needs room for the step sizes and decays of %d tokens", n_tokens);
+  ssm_steps_kernel<<<(n_tokens * H + 255) / 256, 256, 0, stream>>>(u, ldu, dt_off, dt_bias, A_log, dta, n_tokens, H);
+  EL_LAUNCH_CHECK("ssm_steps");
   const dim3 grid(n_seqs * H, (P + SCAN_WARPS - 1) / SCAN_WARPS), block(SCAN_WARPS * 32);
-#define EL_SCAN(NK, U) ssm_scan_kernel<NK, U><<<grid, block, 0, stream>>>(xbc, C, inner, G, N, u, ldu, dt_off, dt_bias, A_log, Dp, state, y, seq_tok0, seq_slot, H, P)
-  if (N <= 32) EL_SCAN(1, 8);
-  else if (N <= 64) EL_SCAN(2, 4);
-  else if (N <= 128) EL_SCAN(4, 4);
-  else EL_SCAN(8, 2);
+  // B and C rows as 16-byte pieces where every row starts on such a boundary
+  const int vec = (uintptr_t)xbc % 16 == 0 && C % 4 == 0 && inner % 4 == 0 && N % 4 == 0;
+  const int slot = 2 * ((N + 3) & ~3) + SCAN_WARPS + 4;
+  const size_t stage_bytes = (size_t)SCAN_CHUNK * slot * sizeof(float);
+  int stages = (int)((44 * 1024) / stage_bytes);
+  stages = stages > SCAN_MAX_STAGES ? SCAN_MAX_STAGES : stages;
+  EL_REFUSE(stages >= 2, "ssm_scan: a state of %d rows does not leave room for two stages of inputs", N);
+#define EL_SCAN(NK) do { if (N == 32 * NK) ssm_scan_kernel<NK, true><<<grid, block, stages * stage_bytes, stream>>>(xbc, C, inner, G, N, u, ldu, dta, Dp, state, y, seq_tok0, seq_slot, H, P, conv_state, conv_off, taps, vec, stages); \
+    else ssm_scan_kernel<NK, false><<<grid, block, stages * stage_bytes, stream>>>(xbc, C, inner, G, N, u, ldu, dta, Dp, state, y, seq_tok0, seq_slot, H, P, conv_state, conv_off, taps, vec, stages); } while (0)
+  if (N <= 32) EL_SCAN(1);
+  else if (N <= 64) EL_SCAN(2);
+  else if (N <= 128) EL_SCAN(4);
+  else EL_SCAN(8);
 #undef EL_SCAN
   EL_LAUNCH_CHECK("ssm_scan");
   return 0;

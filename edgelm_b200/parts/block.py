@@ -163,8 +163,7 @@ class SublayerNormBlock(Part):
             if self.shift is not None:
                 state = cache["shift"].state
                 with ctx.prof("token_shift"):
-                    ops.shift_mix(x, state, self.shift, h.view(1, T, self.hidden), ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots)
-                    ops.save_last_rows(x, state, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs)
+                    ops.shift_mix(x, state, self.shift, h.view(1, T, self.hidden), ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots, move_state=True)
                 mixer_in = h
             elif self.dtype == torch.float32:
                 mixer_in = x

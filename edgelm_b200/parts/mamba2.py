@@ -82,6 +82,7 @@ class Mamba2(Part):
     def workspace_bytes(self, n_tokens, n_seqs):
         f32 = torch.float32
         return (nbytes((n_tokens, self.d_in), f32) + nbytes((n_tokens, self.channels), f32) + nbytes((n_tokens, self.inner), f32) +
+                nbytes((2 * n_tokens * self.heads,), f32) +
                 nbytes((n_tokens, self.inner), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype))
 
     def forward(self, ctx, h, x, cache, accumulate=True):
@@ -92,11 +93,14 @@ class Mamba2(Part):
             linear.matmul(ctx, h, self.w_in, u, prefetch=(self.w_o,))
         xbc = ws.alloc((T, self.channels), f32)
         with ctx.prof("ssm_conv"):
-            ops.conv_silu(u, self.inner, self.conv_w, self.conv_b, cache["conv"].state, xbc, ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs)
+            ops.conv_silu(u, self.inner, self.conv_w, self.conv_b, cache["conv"].state, xbc, ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs,
+                          update_state=False)     # (the scan kernel moves the tail on)
         y = ws.alloc((T, self.inner), f32)
+        steps = ws.alloc((2 * T * self.heads,), f32)
         with ctx.prof("ssm_scan"):
             ops.ssm_scan(xbc, u, 2 * self.inner + 2 * self.groups * self.n_state, self.dt_bias, self.a_log, self.d, cache["ssm"].state, y,
-                         ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs, self.heads, self.groups, self.n_state, self.head_dim)
+                         ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs, self.heads, self.groups, self.n_state, self.head_dim,
+                         conv_state=cache["conv"].state, conv_off=self.inner, scratch=steps)
         yn = ws.alloc((T, self.inner), self.dtype)
         with ctx.prof("ssm_gate_norm"):
             ops.gated_group_norm(y, u[:, :self.inner], self.norm_w, yn, self.norm_groups, self.eps, gate_first=True)

@@ -82,8 +82,7 @@ class DecayTimeMix(Part):
         blends = ws.alloc((5, T, self.hidden), self.dtype)
         last = cache["last"].state
         with ctx.prof("timemix_blend"):
-            ops.shift_mix(h, last, self.mu, blends, ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots)
-            ops.save_last_rows(h, last, ctx.seq_tok0, ctx.seq_slots, ctx.n_seqs)
+            ops.shift_mix(h, last, self.mu, blends, ctx.tok_seq, ctx.seq_tok0, ctx.seq_slots, move_state=True)
         proj = {}
         with ctx.prof("timemix_proj"):
             for i, s in enumerate(("r", "k", "v", "g")):
