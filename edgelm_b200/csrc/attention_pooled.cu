@@ -183,7 +183,8 @@ constexpr int PW_MAX_WARPS = 8;
 // Dynamic shared memory: the query (dk floats, 16-byte aligned), then per warp its maximum, its denominator and dv values.
 // (Eight lanes sharing a key, so that a load instruction of the warp covers four whole rows, was built and measured: 5.2 ms
 // against 3.8 ms for 2,048 tokens of 32 heads with a window of 1,024: the extra shuffles cost more than the loads save.)
-template <typename T>
+// DVR: how many pairs of value dimensions a lane holds (value heads of up to 64 DVR dimensions).
+template <typename T, int DVR>
 __global__ void __launch_bounds__(PW_MAX_WARPS * 32)
 pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
                           const float* __restrict__ pk, const float* __restrict__ pv, const int32_t* __restrict__ tok_pos,
@@ -207,33 +208,29 @@ pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T*
   const int n_blocks = (P > 0 && pos - window >= 0) ? (pos - window + 1) / P : 0;
   const int blk_chunks = (n_blocks + 31) >> 5, n_chunks = blk_chunks + ((n_win + 31) >> 5);
   float m = -INFINITY, l = 0.f;
-  float o[8];                      // dimensions 2 lane + 64 r and the one after it
+  float o[2 * DVR];                // dimensions 2 lane + 64 r and the one after it
 #pragma unroll
-  for (int r = 0; r < 8; ++r) o[r] = 0.f;
+  for (int r = 0; r < 2 * DVR; ++r) o[r] = 0.f;
   for (int c = warp; c < n_chunks; c += NW) {
     const bool pooled = c < blk_chunks;
     const int e0 = pooled ? c * 32 : (c - blk_chunks) * 32;
     const int n_here = min(32, (pooled ? n_blocks : n_win) - e0);
     float sc = -INFINITY;
-    long long voff = -1;           // this lane's key: the offset of its value row
-    if (pooled) {
-      if (lane < n_here) {
+    int vrow = -1;                 // this lane's key: the row of its value
+    if (lane < n_here) {
+      if (pooled) {
         const int e = e0 + lane, end = e * P + P - 1;
         const int page = table[end / PAGE];
         if (page >= 0 && page < n_pages) {
-          const size_t rowi = ((size_t)page * G + g) * R + (e - (PAGE * (end / PAGE)) / P);
-          sc = dot_row<float>(qh, pk + rowi * dk, dk, (dk & 3) == 0);
-          voff = (long long)(rowi * dv);
+          vrow = (page * G + g) * R + (e - (PAGE * (end / PAGE)) / P);
+          sc = dot_row<float>(qh, pk + (size_t)vrow * dk, dk, (dk & 3) == 0);
         }
-      }
-    } else {
-      if (lane < n_here) {
+      } else {
         const int p = lo + e0 + lane;
         const int page = table[p / PAGE];
         if (page >= 0 && page < n_pages) {
-          const size_t rowi = ((size_t)page * G + g) * PAGE + p % PAGE;
-          voff = (long long)(rowi * dv);
-          sc = dot_row<T>(qh, kcache + rowi * dk, dk, vec_k != 0);
+          vrow = (page * G + g) * PAGE + p % PAGE;
+          sc = dot_row<T>(qh, kcache + (size_t)vrow * dk, dk, vec_k != 0);
         }
       }
     }
@@ -244,26 +241,33 @@ pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T*
     l = l * corr + warp_sum(w);
     m = m_new;
 #pragma unroll
-    for (int r = 0; r < 8; ++r) o[r] *= corr;
-    for (int j = 0; j < n_here; ++j) {
-      const float wj = __shfl_sync(0xffffffffu, w, j);
-      const long long vo = __shfl_sync(0xffffffffu, voff, j);
-      if (vo < 0) continue;
-      if (pooled) {
-        const float* vr = pv + vo;
+    for (int r = 0; r < 2 * DVR; ++r) o[r] *= corr;
+    if (pooled) {
+      const bool pair = (dv & 1) == 0;
+      for (int j = 0; j < n_here; ++j) {
+        const float wj = __shfl_sync(0xffffffffu, w, j);
+        const int vr_i = __shfl_sync(0xffffffffu, vrow, j);
+        if (vr_i < 0) continue;
+        const float* vr = pv + (size_t)vr_i * dv;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < DVR; ++r) {
           const int d = 2 * lane + 64 * r;
           if (d < dv) {
-            const float2 x = load_pair(vr + d, (dv & 1) == 0);
+            const float2 x = load_pair(vr + d, pair);
             o[2 * r] = fmaf(wj, x.x, o[2 * r]);
-            if (d + 1 < dv) o[2 * r + 1] = fmaf(wj, (dv & 1) == 0 ? x.y : vr[d + 1], o[2 * r + 1]);
+            if (d + 1 < dv) o[2 * r + 1] = fmaf(wj, pair ? x.y : vr[d + 1], o[2 * r + 1]);
           }
         }
-      } else {
-        const T* vr = vcache + vo;
+      }
+    } else {
+#pragma unroll 4
+      for (int j = 0; j < n_here; ++j) {
+        const float wj = __shfl_sync(0xffffffffu, w, j);
+        const int vr_i = __shfl_sync(0xffffffffu, vrow, j);
+        if (vr_i < 0) continue;
+        const T* vr = vcache + (size_t)vr_i * dv;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < DVR; ++r) {
           const int d = 2 * lane + 64 * r;
           if (d < dv) {
             const float2 x = load_pair(vr + d, pair_v != 0);
@@ -277,7 +281,7 @@ pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T*
   // merge the warps' partial results in a fixed order
   if (lane == 0) { wm[warp] = m; wl[warp] = l; }
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
+  for (int r = 0; r < DVR; ++r) {
     const int d = 2 * lane + 64 * r;
     if (d < dv) wo[warp * dv + d] = o[2 * r];
     if (d + 1 < dv) wo[warp * dv + d + 1] = o[2 * r + 1];
@@ -352,15 +356,17 @@ extern "C" int edgelm_pooled_window_attn(const void* q, void* out, const void* k
   const int vec_k = ((size_t)dk * esz) % 16 == 0 && (uintptr_t)kcache % 16 == 0;
   const int pair_v = dv % 2 == 0 && (uintptr_t)vcache % 8 == 0;
   EL_REFUSE(P == 0 || ((uintptr_t)pk % 16 == 0 && (uintptr_t)pv % 8 == 0), "pooled_window_attn: the pooled rows are not 16-byte aligned");
-  if (dtype == DT_F32)
-    pooled_window_attn_kernel<float><<<grid, block, smem, stream>>>((const float*)q, (float*)out, (const float*)kcache, (const float*)vcache, pk, pv, tok_pos,
-                                                                    tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, window, P, R, vec_k, pair_v);
-  else if (dtype == DT_BF16)
-    pooled_window_attn_kernel<__nv_bfloat16><<<grid, block, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kcache,
-                                                                            (const __nv_bfloat16*)vcache, pk, pv, tok_pos, tok_seq, page_table, table_stride,
-                                                                            n_pages, H, G, dk, dv, scale, window, P, R, vec_k, pair_v);
-  else
+  EL_REFUSE((long long)n_pages * G * (PAGE > R ? PAGE : R) < (1ll << 31), "pooled_window_attn: more cache rows than a 32-bit index counts");
+  const int dvr = dv <= 64 ? 1 : (dv <= 128 ? 2 : 4);
+#define EL_PWA(TT, DVR) pooled_window_attn_kernel<TT, DVR><<<grid, block, smem, stream>>>((const TT*)q, (TT*)out, (const TT*)kcache, (const TT*)vcache, pk, pv, \
+      tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, window, P, R, vec_k, pair_v)
+  if (dtype == DT_F32) {
+    if (dvr == 1) EL_PWA(float, 1); else if (dvr == 2) EL_PWA(float, 2); else EL_PWA(float, 4);
+  } else if (dtype == DT_BF16) {
+    if (dvr == 1) EL_PWA(__nv_bfloat16, 1); else if (dvr == 2) EL_PWA(__nv_bfloat16, 2); else EL_PWA(__nv_bfloat16, 4);
+  } else
     EL_REFUSE(false, "pooled_window_attn: unknown dtype code %d", dtype);
+#undef EL_PWA
   EL_LAUNCH_CHECK("pooled_window_attn");
   return 0;
 }

@@ -300,7 +300,7 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ kk, const
                 const int32_t* __restrict__ seq_tok0, const int32_t* __restrict__ seq_slot, int H, int K) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int s = blockIdx.x / H, h = blockIdx.x - s * H;
-  const int j = blockIdx.y * SCAN_WARPS + warp;
+  const int j = blockIdx.y * (blockDim.x >> 5) + warp;
   if (j >= K) return;
   const int t0 = seq_tok0[s], t1 = seq_tok0[s + 1];
   float* sp = state + (((size_t)seq_slot[s] * H + h) * K + j) * K;
@@ -529,7 +529,9 @@ extern "C" int edgelm_wkv_scan(const float* r, const float* k, const float* v, c
   if (n_seqs == 0) return 0;
   EL_REFUSE(n_seqs > 0 && H > 0, "wkv_scan: bad sizes");
   EL_REFUSE(K >= 1 && K <= 256, "wkv_scan: a head size of %d is not taken (1 to 256)", K);
-  const dim3 grid(n_seqs * H, (K + SCAN_WARPS - 1) / SCAN_WARPS), block(SCAN_WARPS * 32);
+  // a warp a column, whatever the block: with few (sequence, head) pairs, blocks of two warps spread the columns over more SMs
+  const int warps = (long long)n_seqs * H * ((K + SCAN_WARPS - 1) / SCAN_WARPS) >= 2 * 148 ? SCAN_WARPS : 2;
+  const dim3 grid(n_seqs * H, (K + warps - 1) / warps), block(warps * 32);
 #define EL_SCAN(NK, U) wkv_scan_kernel<NK, U><<<grid, block, 0, stream>>>(r, k, v, w, bonus, state, o, seq_tok0, seq_slot, H, K)
   if (K <= 32) EL_SCAN(1, 8);
   else if (K <= 64) EL_SCAN(2, 4);
