@@ -28,6 +28,8 @@ qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restric
                            const int32_t* __restrict__ page_table, int table_stride, int n_pages, T* __restrict__ kcache,
                            T* __restrict__ vcache, int H, int G, int dk, int dv, int rot, const double* __restrict__ freq,
                            float eps, int unit_norm, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   extern __shared__ float stage[];   // PW_WARPS rows of dk floats
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = tok_pos[t];
@@ -96,6 +98,8 @@ __global__ void pool_blocks_kernel(const int32_t* __restrict__ tok_pos, const in
                                    const int32_t* __restrict__ page_table, int table_stride, int n_pages,
                                    const T* __restrict__ kcache, const T* __restrict__ vcache, float* __restrict__ pk,
                                    float* __restrict__ pv, int G, int dk, int dv, int P, int R, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int t = blockIdx.x;
   const int pos = tok_pos[t];
   if (pos < 0 || (pos + 1) % P != 0) return;
@@ -190,6 +194,8 @@ pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T*
                           const float* __restrict__ pk, const float* __restrict__ pv, const int32_t* __restrict__ tok_pos,
                           const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table, int table_stride,
                           int n_pages, int H, int G, int dk, int dv, float scale, int window, int P, int R, int vec_k, int pair_v) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   extern __shared__ __align__(16) float smem[];
   const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
   const int dkp = (dk + 3) & ~3;
@@ -314,10 +320,10 @@ extern "C" int edgelm_qk_rope_norm_append(const float* qkv, const float* bias, v
   EL_REFUSE(rot >= 0 && rot <= dk && rot % 2 == 0, "qk_rope_norm_append: %d rotated dimensions of %d", rot, dk);
   const size_t smem = (size_t)PW_WARPS * dk * sizeof(float);
   if (dtype == DT_F32)
-    qk_rope_norm_append_kernel<float><<<n_tokens, PW_WARPS * 32, smem, stream>>>(qkv, bias, (float*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
+    launch_pdl(pdl_bit_for_tokens(n_tokens), qk_rope_norm_append_kernel<float>, dim3(n_tokens), dim3(PW_WARPS * 32), (size_t)(smem), stream, qkv, bias, (float*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
                                                                               (float*)kcache, (float*)vcache, H, G, dk, dv, rot, freq, eps, unit_norm, err);
   else if (dtype == DT_BF16)
-    qk_rope_norm_append_kernel<__nv_bfloat16><<<n_tokens, PW_WARPS * 32, smem, stream>>>(qkv, bias, (__nv_bfloat16*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
+    launch_pdl(pdl_bit_for_tokens(n_tokens), qk_rope_norm_append_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(PW_WARPS * 32), (size_t)(smem), stream, qkv, bias, (__nv_bfloat16*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
                                                                                       (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, freq, eps, unit_norm, err);
   else
     EL_REFUSE(false, "qk_rope_norm_append: unknown dtype code %d", dtype);
@@ -331,9 +337,9 @@ extern "C" int edgelm_pool_blocks(const int32_t* tok_pos, const int32_t* tok_seq
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && G > 0 && dk > 0 && dv > 0 && P >= 1 && R == (PAGE + P - 1) / P, "pool_blocks: bad sizes (block %d, rows a page %d)", P, R);
   if (dtype == DT_F32)
-    pool_blocks_kernel<float><<<n_tokens, 128, 0, stream>>>(tok_pos, tok_seq, page_table, table_stride, n_pages, (const float*)kcache, (const float*)vcache, pk, pv, G, dk, dv, P, R, err);
+    launch_pdl(pdl_bit_for_tokens(n_tokens), pool_blocks_kernel<float>, dim3(n_tokens), dim3(128), (size_t)(0), stream, tok_pos, tok_seq, page_table, table_stride, n_pages, (const float*)kcache, (const float*)vcache, pk, pv, G, dk, dv, P, R, err);
   else if (dtype == DT_BF16)
-    pool_blocks_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>(tok_pos, tok_seq, page_table, table_stride, n_pages, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, pk, pv, G, dk, dv, P, R, err);
+    launch_pdl(pdl_bit_for_tokens(n_tokens), pool_blocks_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), (size_t)(0), stream, tok_pos, tok_seq, page_table, table_stride, n_pages, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, pk, pv, G, dk, dv, P, R, err);
   else
     EL_REFUSE(false, "pool_blocks: unknown dtype code %d", dtype);
   EL_LAUNCH_CHECK("pool_blocks");
@@ -358,7 +364,7 @@ extern "C" int edgelm_pooled_window_attn(const void* q, void* out, const void* k
   EL_REFUSE(P == 0 || ((uintptr_t)pk % 16 == 0 && (uintptr_t)pv % 8 == 0), "pooled_window_attn: the pooled rows are not 16-byte aligned");
   EL_REFUSE((long long)n_pages * G * (PAGE > R ? PAGE : R) < (1ll << 31), "pooled_window_attn: more cache rows than a 32-bit index counts");
   const int dvr = dv <= 64 ? 1 : (dv <= 128 ? 2 : 4);
-#define EL_PWA(TT, DVR) pooled_window_attn_kernel<TT, DVR><<<grid, block, smem, stream>>>((const TT*)q, (TT*)out, (const TT*)kcache, (const TT*)vcache, pk, pv, \
+#define EL_PWA(TT, DVR) launch_pdl(pdl_bit_for_tokens(n_tokens), pooled_window_attn_kernel<TT, DVR>, dim3(grid), dim3(block), (size_t)(smem), stream, (const TT*)q, (TT*)out, (const TT*)kcache, (const TT*)vcache, pk, pv, \
       tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, window, P, R, vec_k, pair_v)
   if (dtype == DT_F32) {
     if (dvr == 1) EL_PWA(float, 1); else if (dvr == 2) EL_PWA(float, 2); else EL_PWA(float, 4);

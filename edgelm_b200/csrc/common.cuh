@@ -82,9 +82,14 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // Bit mask of the kernel families launched as programmatic dependent launches (1: few-rows matrix
-// products, 2: decode attention, 4: unused, 8: one-tile tcgen05 matrix products, 16: tcgen05 prefill attention, 32: RMSNorm,
+// products, 2: decode attention, 4: unused, 8: one-tile tcgen05 matrix products, 16: tcgen05 prefill attention, 32: RMSNorm, the kernels of the state mixers and of the window attention with pooled blocks,
 // the vectorised rotation and cache append, the persistent tcgen05 matrix products); 0: ordinary launches everywhere.
 int pdl_enabled();
+
+// The kernels of the state mixers and of the window attention are launched as programmatic dependents in steps of few
+// tokens only (decode steps: 0.642 -> 0.622 ms a step of 8 sequences at a width of 576); in prompt steps their waiting
+// blocks sat beside long-running kernels and cost more than the earlier start gave (4.73 -> 5.35 ms for 2,048 tokens).
+inline int pdl_bit_for_tokens(int n_tokens) { return n_tokens <= 64 ? 32 : 0; }
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(int bit, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {

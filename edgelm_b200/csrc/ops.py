@@ -521,7 +521,7 @@ def wkv_scan(r, k, v, w, bonus, state, o, seq_tok0, seq_slot, n_seqs, heads, hea
     _need(r.shape == k.shape == v.shape == w.shape == o.shape and r.shape[1] == heads * head_dim, "wkv_scan: shapes")
     _need(tuple(state.shape[1:]) == (heads, head_dim, head_dim) and bonus.numel() == heads * head_dim, "wkv_scan: state or bonus")
     _check(lib().edgelm_wkv_scan(_p(r), _p(k), _p(v), _p(w), _p(bonus), _p(state), _p(o), _p(seq_tok0), _p(seq_slot), int(n_seqs),
-                                 heads, head_dim, _stream()))
+                                 heads, head_dim, r.shape[0], _stream()))
 
 
 def lowrank_decay(a, w2, w0, out):

@@ -24,6 +24,8 @@ template <typename TIn, typename TOut>
 __global__ void shift_mix_kernel(const TIn* __restrict__ in, const float* state, const float* __restrict__ mu,
                                  TOut* __restrict__ out, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_tok0,
                                  const int32_t* __restrict__ seq_slot, int n_tokens, int dim, int n_mix, int move_state) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int t = blockIdx.x;
   const int s = tok_seq[t];
   const bool first = t == seq_tok0[s];
@@ -43,6 +45,8 @@ __global__ void shift_mix_kernel(const TIn* __restrict__ in, const float* state,
 template <typename TIn>
 __global__ void save_last_rows_kernel(const TIn* __restrict__ in, float* __restrict__ state, const int32_t* __restrict__ seq_tok0,
                                       const int32_t* __restrict__ seq_slot, int dim) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int s = blockIdx.x;
   const int t = seq_tok0[s + 1] - 1;
   float* st = state + (size_t)seq_slot[s] * dim;
@@ -57,6 +61,8 @@ __global__ void conv_silu_kernel(const float* __restrict__ u, int ldu, int off, 
                                  const float* __restrict__ b, const float* __restrict__ state, float* __restrict__ out,
                                  const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ seq_tok0,
                                  const int32_t* __restrict__ seq_slot, int C, int taps) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int t = blockIdx.x;
   const int s = tok_seq[t];
   const int t0 = seq_tok0[s];
@@ -77,6 +83,8 @@ __global__ void conv_silu_kernel(const float* __restrict__ u, int ldu, int off, 
 // rows upwards, so that a row it still has to read (one further on) is never overwritten before.
 __global__ void conv_state_update_kernel(const float* __restrict__ u, int ldu, int off, float* __restrict__ state,
                                          const int32_t* __restrict__ seq_tok0, const int32_t* __restrict__ seq_slot, int C, int taps) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int s = blockIdx.x;
   const int t0 = seq_tok0[s], n = seq_tok0[s + 1] - t0;
   float* st = state + (size_t)seq_slot[s] * (taps - 1) * C;
@@ -113,6 +121,8 @@ __device__ __forceinline__ float warp_sums(float (&acc)[U], int lane) {
 // dta[t][h] = dt, dta[t][H + h] = decay.
 __global__ void ssm_steps_kernel(const float* __restrict__ u, int ldu, int dt_off, const float* __restrict__ dt_bias,
                                  const float* __restrict__ A_log, float* __restrict__ dta, int n_tokens, int H) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_tokens * H) return;
   const int t = i / H, h = i - t * H;
@@ -155,6 +165,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, int C, int inner, int G, int N, c
                 float* __restrict__ state, float* __restrict__ y, const int32_t* __restrict__ seq_tok0,
                 const int32_t* __restrict__ seq_slot, int H, int P, float* __restrict__ conv_state, int conv_off, int taps, int vec,
                 int stages) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   extern __shared__ __align__(16) float ring[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int s = blockIdx.x / H, h = blockIdx.x - s * H;
@@ -298,6 +310,8 @@ __global__ void __launch_bounds__(SCAN_WARPS * 32)
 wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ kk, const float* __restrict__ v, const float* __restrict__ w,
                 const float* __restrict__ bonus, float* __restrict__ state, float* __restrict__ o,
                 const int32_t* __restrict__ seq_tok0, const int32_t* __restrict__ seq_slot, int H, int K) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int s = blockIdx.x / H, h = blockIdx.x - s * H;
   const int j = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -365,6 +379,8 @@ wkv_scan_kernel(const float* __restrict__ r, const float* __restrict__ kk, const
 template <typename TW>
 __global__ void lowrank_decay_kernel(const float* __restrict__ a, const TW* __restrict__ w2, const float* __restrict__ w0,
                                      float* __restrict__ out, int C, int L) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   extern __shared__ float th[];
   const int t = blockIdx.x;
   for (int l = threadIdx.x; l < L; l += blockDim.x) th[l] = tanhf(a[(size_t)t * L + l]);
@@ -385,6 +401,8 @@ template <typename TOut>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ gate, int ldg,
                                         const float* __restrict__ w, TOut* __restrict__ out, int inner, int groups, float eps,
                                         int gate_first) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   __shared__ float red[33];
   const int t = blockIdx.x, g = blockIdx.y, gs = inner / groups;
   const float* yr = y + (size_t)t * inner + (size_t)g * gs;
@@ -408,6 +426,8 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const float
 template <typename TCast>
 __global__ void rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y1, float a, const float* __restrict__ y2, float b,
                                    const float* __restrict__ w, TCast* __restrict__ xc, int dim, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   __shared__ float red[33];
   const int t = blockIdx.x;
   const float* r1 = y1 + (size_t)t * dim;
@@ -430,6 +450,8 @@ __global__ void rmsnorm_add_kernel(float* __restrict__ x, const float* __restric
 
 // out = a y1 + b y2
 __global__ void scaled_sum_kernel(const float* __restrict__ y1, float a, const float* __restrict__ y2, float b, float* __restrict__ out, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();   // (launched as a programmatic dependent: nothing is read or written before the kernel ahead is done)
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) out[i] = a * y1[i] + b * y2[i];
 }
 
@@ -454,7 +476,7 @@ extern "C" int edgelm_shift_mix(const void* in, int in_dtype, float* state, cons
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && dim > 0 && n_mix > 0, "shift_mix: bad sizes tokens=%d dim=%d mixes=%d", n_tokens, dim, n_mix);
   const dim3 grid(n_tokens), block(row_threads(dim));
-#define EL_SM(TI, TO) shift_mix_kernel<TI, TO><<<grid, block, 0, stream>>>((const TI*)in, state, mu, (TO*)out, tok_seq, seq_tok0, seq_slot, n_tokens, dim, n_mix, move_state)
+#define EL_SM(TI, TO) launch_pdl(pdl_bit_for_tokens(n_tokens), shift_mix_kernel<TI, TO>, dim3(grid), dim3(block), (size_t)(0), stream, (const TI*)in, state, mu, (TO*)out, tok_seq, seq_tok0, seq_slot, n_tokens, dim, n_mix, move_state)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) EL_SM(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) EL_SM(float, __nv_bfloat16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) EL_SM(__nv_bfloat16, __nv_bfloat16);
@@ -468,8 +490,9 @@ extern "C" int edgelm_save_last_rows(const void* in, int in_dtype, float* state,
                                      int n_seqs, int dim, cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   EL_REFUSE(n_seqs > 0 && dim > 0, "save_last_rows: bad sizes");
-  if (in_dtype == DT_F32) save_last_rows_kernel<float><<<n_seqs, row_threads(dim), 0, stream>>>((const float*)in, state, seq_tok0, seq_slot, dim);
-  else if (in_dtype == DT_BF16) save_last_rows_kernel<__nv_bfloat16><<<n_seqs, row_threads(dim), 0, stream>>>((const __nv_bfloat16*)in, state, seq_tok0, seq_slot, dim);
+  const int n_tokens = n_seqs;   // (as many launches' worth of blocks as a decode step has tokens)
+  if (in_dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_tokens), save_last_rows_kernel<float>, dim3(n_seqs), dim3(row_threads(dim)), (size_t)(0), stream, (const float*)in, state, seq_tok0, seq_slot, dim);
+  else if (in_dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_tokens), save_last_rows_kernel<__nv_bfloat16>, dim3(n_seqs), dim3(row_threads(dim)), (size_t)(0), stream, (const __nv_bfloat16*)in, state, seq_tok0, seq_slot, dim);
   else EL_REFUSE(false, "save_last_rows: unknown dtype code %d", in_dtype);
   EL_LAUNCH_CHECK("save_last_rows");
   return 0;
@@ -481,10 +504,10 @@ extern "C" int edgelm_conv_silu(const float* u, int ldu, int off, const float* w
                                 int C, int taps, int update_state, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && n_seqs > 0 && C > 0 && taps >= 1 && off >= 0 && off + C <= ldu, "conv_silu: bad sizes C=%d taps=%d", C, taps);
-  conv_silu_kernel<<<n_tokens, row_threads(C), 0, stream>>>(u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps);
+  launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps);
   EL_LAUNCH_CHECK("conv_silu");
   if (taps > 1 && update_state) {
-    conv_state_update_kernel<<<dim3(n_seqs, (C + 255) / 256), 256, 0, stream>>>(u, ldu, off, state, seq_tok0, seq_slot, C, taps);
+    launch_pdl(pdl_bit_for_tokens(n_tokens), conv_state_update_kernel, dim3(dim3(n_seqs, (C + 255) / 256)), dim3(256), (size_t)(0), stream, u, ldu, off, state, seq_tok0, seq_slot, C, taps);
     EL_LAUNCH_CHECK("conv_state_update");
   }
   return 0;
@@ -502,7 +525,7 @@ extern "C" int edgelm_ssm_scan(const float* xbc, int C, int inner, int G, int N,
             "ssm_scan: sizes do not fit (heads %d, groups %d, head size %d, inner %d, channels %d)", H, G, P, inner, C);
   EL_REFUSE(N >= 1 && N <= 256, "ssm_scan: a state of %d rows per head is not taken (1 to 256)", N);
   EL_REFUSE(dta != nullptr && n_tokens > 0, "ssm_scan: needs room for the step sizes and decays of %d tokens", n_tokens);
-  ssm_steps_kernel<<<(n_tokens * H + 255) / 256, 256, 0, stream>>>(u, ldu, dt_off, dt_bias, A_log, dta, n_tokens, H);
+  launch_pdl(pdl_bit_for_tokens(n_tokens), ssm_steps_kernel, dim3((n_tokens * H + 255) / 256), dim3(256), (size_t)(0), stream, u, ldu, dt_off, dt_bias, A_log, dta, n_tokens, H);
   EL_LAUNCH_CHECK("ssm_steps");
   const dim3 grid(n_seqs * H, (P + SCAN_WARPS - 1) / SCAN_WARPS), block(SCAN_WARPS * 32);
   // B and C rows as 16-byte pieces where every row starts on such a boundary
@@ -512,8 +535,8 @@ extern "C" int edgelm_ssm_scan(const float* xbc, int C, int inner, int G, int N,
   int stages = (int)((44 * 1024) / stage_bytes);
   stages = stages > SCAN_MAX_STAGES ? SCAN_MAX_STAGES : stages;
   EL_REFUSE(stages >= 2, "ssm_scan: a state of %d rows does not leave room for two stages of inputs", N);
-#define EL_SCAN(NK) do { if (N == 32 * NK) ssm_scan_kernel<NK, true><<<grid, block, stages * stage_bytes, stream>>>(xbc, C, inner, G, N, u, ldu, dta, Dp, state, y, seq_tok0, seq_slot, H, P, conv_state, conv_off, taps, vec, stages); \
-    else ssm_scan_kernel<NK, false><<<grid, block, stages * stage_bytes, stream>>>(xbc, C, inner, G, N, u, ldu, dta, Dp, state, y, seq_tok0, seq_slot, H, P, conv_state, conv_off, taps, vec, stages); } while (0)
+#define EL_SCAN(NK) do { if (N == 32 * NK) launch_pdl(pdl_bit_for_tokens(n_tokens), ssm_scan_kernel<NK, true>, dim3(grid), dim3(block), (size_t)(stages * stage_bytes), stream, xbc, C, inner, G, N, u, ldu, dta, Dp, state, y, seq_tok0, seq_slot, H, P, conv_state, conv_off, taps, vec, stages); \
+    else launch_pdl(pdl_bit_for_tokens(n_tokens), ssm_scan_kernel<NK, false>, dim3(grid), dim3(block), (size_t)(stages * stage_bytes), stream, xbc, C, inner, G, N, u, ldu, dta, Dp, state, y, seq_tok0, seq_slot, H, P, conv_state, conv_off, taps, vec, stages); } while (0)
   if (N <= 32) EL_SCAN(1);
   else if (N <= 64) EL_SCAN(2);
   else if (N <= 128) EL_SCAN(4);
@@ -524,7 +547,7 @@ extern "C" int edgelm_ssm_scan(const float* xbc, int C, int inner, int G, int N,
 }
 
 extern "C" int edgelm_wkv_scan(const float* r, const float* k, const float* v, const float* w, const float* bonus, float* state,
-                               float* o, const int32_t* seq_tok0, const int32_t* seq_slot, int n_seqs, int H, int K,
+                               float* o, const int32_t* seq_tok0, const int32_t* seq_slot, int n_seqs, int H, int K, int n_tokens,
                                cudaStream_t stream) {
   if (n_seqs == 0) return 0;
   EL_REFUSE(n_seqs > 0 && H > 0, "wkv_scan: bad sizes");
@@ -532,7 +555,7 @@ extern "C" int edgelm_wkv_scan(const float* r, const float* k, const float* v, c
   // a warp a column, whatever the block: with few (sequence, head) pairs, blocks of two warps spread the columns over more SMs
   const int warps = (long long)n_seqs * H * ((K + SCAN_WARPS - 1) / SCAN_WARPS) >= 2 * 148 ? SCAN_WARPS : 2;
   const dim3 grid(n_seqs * H, (K + warps - 1) / warps), block(warps * 32);
-#define EL_SCAN(NK, U) wkv_scan_kernel<NK, U><<<grid, block, 0, stream>>>(r, k, v, w, bonus, state, o, seq_tok0, seq_slot, H, K)
+#define EL_SCAN(NK, U) launch_pdl(pdl_bit_for_tokens(n_tokens), wkv_scan_kernel<NK, U>, dim3(grid), dim3(block), (size_t)(0), stream, r, k, v, w, bonus, state, o, seq_tok0, seq_slot, H, K)
   if (K <= 32) EL_SCAN(1, 8);
   else if (K <= 64) EL_SCAN(2, 4);
   else if (K <= 128) EL_SCAN(4, 2);
@@ -547,8 +570,8 @@ extern "C" int edgelm_lowrank_decay(const float* a, const void* w2, int w_dtype,
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && C > 0 && L > 0 && L <= 8192, "lowrank_decay: bad sizes C=%d L=%d", C, L);
   const size_t smem = (size_t)L * sizeof(float);
-  if (w_dtype == DT_F32) lowrank_decay_kernel<float><<<n_tokens, row_threads(C), smem, stream>>>(a, (const float*)w2, w0, out, C, L);
-  else if (w_dtype == DT_BF16) lowrank_decay_kernel<__nv_bfloat16><<<n_tokens, row_threads(C), smem, stream>>>(a, (const __nv_bfloat16*)w2, w0, out, C, L);
+  if (w_dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_tokens), lowrank_decay_kernel<float>, dim3(n_tokens), dim3(row_threads(C)), (size_t)(smem), stream, a, (const float*)w2, w0, out, C, L);
+  else if (w_dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_tokens), lowrank_decay_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(row_threads(C)), (size_t)(smem), stream, a, (const __nv_bfloat16*)w2, w0, out, C, L);
   else EL_REFUSE(false, "lowrank_decay: unknown dtype code %d", w_dtype);
   EL_LAUNCH_CHECK("lowrank_decay");
   return 0;
@@ -559,8 +582,8 @@ extern "C" int edgelm_gated_group_norm(const float* y, const float* gate, int ld
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && inner > 0 && groups > 0 && inner % groups == 0, "gated_group_norm: %d values do not split into %d equal groups", inner, groups);
   const dim3 grid(n_tokens, groups), block(inner / groups >= 1024 ? 256 : (inner / groups >= 128 ? 128 : 32));
-  if (out_dtype == DT_F32) gated_group_norm_kernel<float><<<grid, block, 0, stream>>>(y, gate, ldg, w, (float*)out, inner, groups, eps, gate_first);
-  else if (out_dtype == DT_BF16) gated_group_norm_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(y, gate, ldg, w, (__nv_bfloat16*)out, inner, groups, eps, gate_first);
+  if (out_dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<float>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (float*)out, inner, groups, eps, gate_first);
+  else if (out_dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_tokens), gated_group_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(block), (size_t)(0), stream, y, gate, ldg, w, (__nv_bfloat16*)out, inner, groups, eps, gate_first);
   else EL_REFUSE(false, "gated_group_norm: unknown dtype code %d", out_dtype);
   EL_LAUNCH_CHECK("gated_group_norm");
   return 0;
@@ -572,8 +595,8 @@ extern "C" int edgelm_rmsnorm_add(float* x, const float* y1, float a, const floa
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && dim > 0, "rmsnorm_add: bad sizes");
   const dim3 grid(n_tokens), block(row_threads(dim));
-  if (xc == nullptr || cast_dtype == DT_F32) rmsnorm_add_kernel<float><<<grid, block, 0, stream>>>(x, y1, a, y2, b, w, (float*)xc, dim, eps);
-  else if (cast_dtype == DT_BF16) rmsnorm_add_kernel<__nv_bfloat16><<<grid, block, 0, stream>>>(x, y1, a, y2, b, w, (__nv_bfloat16*)xc, dim, eps);
+  if (xc == nullptr || cast_dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_tokens), rmsnorm_add_kernel<float>, dim3(grid), dim3(block), (size_t)(0), stream, x, y1, a, y2, b, w, (float*)xc, dim, eps);
+  else if (cast_dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_tokens), rmsnorm_add_kernel<__nv_bfloat16>, dim3(grid), dim3(block), (size_t)(0), stream, x, y1, a, y2, b, w, (__nv_bfloat16*)xc, dim, eps);
   else EL_REFUSE(false, "rmsnorm_add: unknown dtype code %d", cast_dtype);
   EL_LAUNCH_CHECK("rmsnorm_add");
   return 0;
