@@ -34,12 +34,12 @@ qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restric
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = tok_pos[t];
   if (pos < 0) {
-    if (threadIdx.x == 0) atomicOr(err, ERR_POSITION_RANGE);
+    if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, ERR_POSITION_RANGE);
     return;
   }
   const int page = page_table[(size_t)tok_seq[t] * table_stride + pos / PAGE];
   if (page < 0 || page >= n_pages) {
-    if (threadIdx.x == 0) atomicOr(err, ERR_PAGE_RANGE);
+    if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, ERR_PAGE_RANGE);
     return;
   }
   const int in_page = pos % PAGE, half = rot >> 1;
@@ -47,7 +47,8 @@ qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restric
   const float* row = qkv + (size_t)t * ld;
   float* sh = stage + warp * dk;
   const double dpos = (double)pos;
-  for (int head = warp; head < H + G; head += PW_WARPS) {   // query heads, then key heads
+  // a warp a head (query heads, then key heads); the blocks of a token stand side by side over the heads
+  for (int head = blockIdx.y * PW_WARPS + warp; head < H + G; head += gridDim.y * PW_WARPS) {
     const float* src = row + (size_t)head * dk;
     const float* b = bias ? bias + (size_t)head * dk : nullptr;
     for (int i = lane; i < dk; i += 32) sh[i] = src[i] + (b ? b[i] : 0.f);
@@ -86,7 +87,7 @@ qk_rope_norm_append_kernel(const float* __restrict__ qkv, const float* __restric
   }
   const float* vrow = row + (size_t)(H + G) * dk;
   const float* vb = bias ? bias + (size_t)(H + G) * dk : nullptr;
-  for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < G * dv; i += gridDim.y * blockDim.x) {
     const int g = i / dv, j = i - g * dv;
     vcache[(((size_t)page * G + g) * PAGE + in_page) * dv + j] = from_f32<T>(vrow[i] + (vb ? vb[i] : 0.f));
   }
@@ -107,17 +108,20 @@ __global__ void pool_blocks_kernel(const int32_t* __restrict__ tok_pos, const in
   const int32_t* table = page_table + (size_t)tok_seq[t] * table_stride;
   const int dst_page = table[pos / PAGE];
   if (dst_page < 0 || dst_page >= n_pages) {
-    if (threadIdx.x == 0) atomicOr(err, ERR_PAGE_RANGE);
+    if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, ERR_PAGE_RANGE);
     return;
   }
   const int rowi = b - (PAGE * (pos / PAGE)) / P;
   const float invP = 1.0f / (float)P;
-  for (int i = threadIdx.x; i < G * (dk + dv); i += blockDim.x) {
-    const bool is_k = i < G * dk;
-    const int e = is_k ? i : i - G * dk, d = is_k ? dk : dv;
-    const int g = e / d, c = e - g * d;
+  // a block per (token that ends a block, key/value head); a thread a channel of the key, then of the value: the rows
+  // of a block lie side by side in a page, so neighbouring threads read neighbouring addresses, eight rows in flight
+  const int g = blockIdx.y;
+  for (int i = threadIdx.x; i < dk + dv; i += blockDim.x) {
+    const bool is_k = i < dk;
+    const int d = is_k ? dk : dv, c = is_k ? i : i - dk;
     const T* base = is_k ? kcache : vcache;
     float acc = 0.f;
+#pragma unroll 8
     for (int j = 0; j < P; ++j) {
       const int p = b * P + j;
       const int page = table[p / PAGE];
@@ -320,10 +324,10 @@ extern "C" int edgelm_qk_rope_norm_append(const float* qkv, const float* bias, v
   EL_REFUSE(rot >= 0 && rot <= dk && rot % 2 == 0, "qk_rope_norm_append: %d rotated dimensions of %d", rot, dk);
   const size_t smem = (size_t)PW_WARPS * dk * sizeof(float);
   if (dtype == DT_F32)
-    launch_pdl(pdl_bit_for_tokens(n_tokens), qk_rope_norm_append_kernel<float>, dim3(n_tokens), dim3(PW_WARPS * 32), (size_t)(smem), stream, qkv, bias, (float*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
+    launch_pdl(pdl_bit_for_tokens(n_tokens), qk_rope_norm_append_kernel<float>, dim3(n_tokens, (H + G + PW_WARPS - 1) / PW_WARPS), dim3(PW_WARPS * 32), (size_t)(smem), stream, qkv, bias, (float*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
                                                                               (float*)kcache, (float*)vcache, H, G, dk, dv, rot, freq, eps, unit_norm, err);
   else if (dtype == DT_BF16)
-    launch_pdl(pdl_bit_for_tokens(n_tokens), qk_rope_norm_append_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(PW_WARPS * 32), (size_t)(smem), stream, qkv, bias, (__nv_bfloat16*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
+    launch_pdl(pdl_bit_for_tokens(n_tokens), qk_rope_norm_append_kernel<__nv_bfloat16>, dim3(n_tokens, (H + G + PW_WARPS - 1) / PW_WARPS), dim3(PW_WARPS * 32), (size_t)(smem), stream, qkv, bias, (__nv_bfloat16*)q_out, tok_pos, tok_seq, page_table, table_stride, n_pages,
                                                                                       (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, freq, eps, unit_norm, err);
   else
     EL_REFUSE(false, "qk_rope_norm_append: unknown dtype code %d", dtype);
@@ -337,9 +341,9 @@ extern "C" int edgelm_pool_blocks(const int32_t* tok_pos, const int32_t* tok_seq
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && G > 0 && dk > 0 && dv > 0 && P >= 1 && R == (PAGE + P - 1) / P, "pool_blocks: bad sizes (block %d, rows a page %d)", P, R);
   if (dtype == DT_F32)
-    launch_pdl(pdl_bit_for_tokens(n_tokens), pool_blocks_kernel<float>, dim3(n_tokens), dim3(128), (size_t)(0), stream, tok_pos, tok_seq, page_table, table_stride, n_pages, (const float*)kcache, (const float*)vcache, pk, pv, G, dk, dv, P, R, err);
+    launch_pdl(pdl_bit_for_tokens(n_tokens), pool_blocks_kernel<float>, dim3(n_tokens, G), dim3(128), (size_t)(0), stream, tok_pos, tok_seq, page_table, table_stride, n_pages, (const float*)kcache, (const float*)vcache, pk, pv, G, dk, dv, P, R, err);
   else if (dtype == DT_BF16)
-    launch_pdl(pdl_bit_for_tokens(n_tokens), pool_blocks_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), (size_t)(0), stream, tok_pos, tok_seq, page_table, table_stride, n_pages, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, pk, pv, G, dk, dv, P, R, err);
+    launch_pdl(pdl_bit_for_tokens(n_tokens), pool_blocks_kernel<__nv_bfloat16>, dim3(n_tokens, G), dim3(128), (size_t)(0), stream, tok_pos, tok_seq, page_table, table_stride, n_pages, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache, pk, pv, G, dk, dv, P, R, err);
   else
     EL_REFUSE(false, "pool_blocks: unknown dtype code %d", dtype);
   EL_LAUNCH_CHECK("pool_blocks");

@@ -557,8 +557,8 @@ extern "C" int edgelm_wkv_scan(const float* r, const float* k, const float* v, c
   const dim3 grid(n_seqs * H, (K + warps - 1) / warps), block(warps * 32);
 #define EL_SCAN(NK, U) launch_pdl(pdl_bit_for_tokens(n_tokens), wkv_scan_kernel<NK, U>, dim3(grid), dim3(block), (size_t)(0), stream, r, k, v, w, bonus, state, o, seq_tok0, seq_slot, H, K)
   if (K <= 32) EL_SCAN(1, 8);
-  else if (K <= 64) EL_SCAN(2, 4);
-  else if (K <= 128) EL_SCAN(4, 2);
+  else if (K <= 64) EL_SCAN(2, 8);
+  else if (K <= 128) EL_SCAN(4, 4);
   else EL_SCAN(8, 1);
 #undef EL_SCAN
   EL_LAUNCH_CHECK("wkv_scan");
