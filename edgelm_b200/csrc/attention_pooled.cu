@@ -310,6 +310,173 @@ pooled_window_attn_kernel(const T* __restrict__ q, T* __restrict__ out, const T*
   }
 }
 
+// ---- the attention kernel of prompt steps
+// A block = up to 32 (token, query head) rows of one key/value head and of one run of consecutive tokens (a tile of the
+// step's metadata); 64 keys with their values are staged in shared memory as float32 once for all the rows: first the
+// pooled rows that the tile's last token sees (gathered through the page table), then the window's pages.  A warp owns
+// four rows, so a key element read from shared memory serves four multiply-adds; lanes own keys for the scores and
+// value dimensions for the weighted sum.  Scores, maxima, exponentials, sums and weighted values are float32.  A row sees
+// pooled block e iff e < its own count of seen blocks, and key p iff first <= p <= its position.
+constexpr int TW_RW = 4, TW_WARPS = 8, TW_ROWS = TW_RW * TW_WARPS, TW_KEYS = PAGE;
+
+template <typename T, int NC>    // NC = ceil(dv / 32): value dimensions a lane owns
+__global__ void __launch_bounds__(TW_WARPS * 32)
+pooled_window_attn_tiled_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
+                                const float* __restrict__ pk, const float* __restrict__ pv, const int32_t* __restrict__ page_table,
+                                int table_stride, int n_pages, const int32_t* __restrict__ tile_seq, const int32_t* __restrict__ tile_tok0,
+                                const int32_t* __restrict__ tile_ntok, const int32_t* __restrict__ tile_pos0, int H, int G, int dk,
+                                int dv, float scale, int window, int P, int R) {
+  extern __shared__ float tw_smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int ks = dk + 1;                        // padded key row: lanes read different rows
+  float* Ks = tw_smem;                          // [TW_KEYS][dk + 1]
+  float* Vs = Ks + TW_KEYS * ks;                // [TW_KEYS][dv]
+  float* Qs = Vs + TW_KEYS * dv;                // [TW_ROWS][dk]
+  float* Ps = Qs + TW_ROWS * dk;                // [TW_ROWS][TW_KEYS]
+  const int tile = blockIdx.x, g = blockIdx.y, grp = H / G;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int seq = tile_seq[tile], tok0 = tile_tok0[tile], ntok = tile_ntok[tile], pos0 = tile_pos0[tile];
+  const int32_t* pages = page_table + (size_t)seq * table_stride;
+  const int rows_total = ntok * grp, row_base = blockIdx.z * TW_ROWS;
+  if (row_base >= rows_total) return;
+  const int rows_here = min(TW_ROWS, rows_total - row_base);
+  const int last_pos = pos0 + (row_base + rows_here - 1) / grp, first_pos = pos0 + row_base / grp;
+  for (int i = threadIdx.x; i < rows_here * dk; i += blockDim.x) {
+    const int r = i / dk, d = i - r * dk;
+    const int rr = row_base + r, tok = rr / grp, head = g * grp + rr % grp;
+    Qs[r * dk + d] = to_f32(q[((size_t)(tok0 + tok) * H + head) * dk + d]);
+  }
+  float m[TW_RW], l[TW_RW], acc[TW_RW][NC];
+  int limit[TW_RW], first[TW_RW], seen[TW_RW];
+#pragma unroll
+  for (int r = 0; r < TW_RW; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+    const int rr = row_base + warp * TW_RW + r;
+    limit[r] = rr < rows_total ? pos0 + rr / grp : -1;                       // the row's own position; -1: no row
+    first[r] = max(0, limit[r] - window + 1);
+    seen[r] = (P > 0 && limit[r] - window >= 0) ? (limit[r] - window + 1) / P : 0;   // pooled blocks wholly before its window
+#pragma unroll
+    for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
+  }
+  // what a warp does with the 64 staged keys whose indices (block numbers, or positions) start at `base`: row r sees
+  // index i iff lo[r] <= i <= hi[r]
+  auto process = [&](int base, const int (&lo)[TW_RW], const int (&hi)[TW_RW], int valid) {
+    int any_hi = -1, any_lo = 0x7fffffff;
+#pragma unroll
+    for (int r = 0; r < TW_RW; ++r)
+      if (hi[r] >= lo[r]) { any_hi = max(any_hi, hi[r]); any_lo = min(any_lo, lo[r]); }
+    if (base > any_hi || base + TW_KEYS - 1 < any_lo) return;     // none of this warp's rows sees any of these keys
+    const int i0 = base + lane, i1 = i0 + 32;
+    float s0[TW_RW] = {}, s1[TW_RW] = {};
+    const float* k0 = Ks + lane * ks;
+    const float* k1 = Ks + (lane + 32) * ks;
+    const float* qw = Qs + warp * TW_RW * dk;
+    for (int d = 0; d < dk; ++d) {
+      const float a = k0[d], b = k1[d];
+#pragma unroll
+      for (int r = 0; r < TW_RW; ++r) {
+        const float qv = qw[r * dk + d];
+        s0[r] = fmaf(qv, a, s0[r]);
+        s1[r] = fmaf(qv, b, s1[r]);
+      }
+    }
+    float corr[TW_RW];
+#pragma unroll
+    for (int r = 0; r < TW_RW; ++r) {
+      const float a = i0 >= lo[r] && i0 <= hi[r] ? s0[r] * scale : -INFINITY;
+      const float b = i1 >= lo[r] && i1 <= hi[r] ? s1[r] * scale : -INFINITY;
+      const float mx = fmaxf(m[r], warp_max(fmaxf(a, b)));
+      float p0 = 0.f, p1 = 0.f;
+      corr[r] = 1.f;
+      if (mx != -INFINITY) {      // uniform over the warp
+        corr[r] = expf(m[r] - mx);
+        p0 = expf(a - mx);
+        p1 = expf(b - mx);
+        l[r] = l[r] * corr[r] + warp_sum(p0 + p1);
+        m[r] = mx;
+      }
+      Ps[(warp * TW_RW + r) * TW_KEYS + lane] = p0;
+      Ps[(warp * TW_RW + r) * TW_KEYS + lane + 32] = p1;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < TW_RW; ++r)
+#pragma unroll
+      for (int c = 0; c < NC; ++c) acc[r][c] *= corr[r];
+    const float* pw = Ps + warp * TW_RW * TW_KEYS;
+    for (int j = 0; j < valid; ++j) {
+      float v[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int d = lane + 32 * c;
+        v[c] = d < dv ? Vs[j * dv + d] : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < TW_RW; ++r) {
+        const float pj = pw[r * TW_KEYS + j];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[r][c] = fmaf(pj, v[c], acc[r][c]);
+      }
+    }
+    __syncwarp();
+  };
+  // 1. the pooled rows that the block's last token sees
+  const int blocks_seen = (P > 0 && last_pos - window >= 0) ? (last_pos - window + 1) / P : 0;
+  int zero[TW_RW], top[TW_RW];
+#pragma unroll
+  for (int r = 0; r < TW_RW; ++r) { zero[r] = 0; top[r] = limit[r] < 0 ? -1 : seen[r] - 1; }
+  for (int e0 = 0; e0 < blocks_seen; e0 += TW_KEYS) {
+    const int valid = min(TW_KEYS, blocks_seen - e0);
+    __syncthreads();              // the keys staged before are no longer read (and the queries are staged)
+    for (int i = threadIdx.x; i < TW_KEYS * (dk + dv); i += blockDim.x) {
+      const int j = i / (dk + dv), c = i - j * (dk + dv);
+      float val = 0.f;
+      if (j < valid) {
+        const int e = e0 + j, end = e * P + P - 1;
+        const int page = pages[end / PAGE];
+        if (page >= 0 && page < n_pages) {
+          const size_t rowi = ((size_t)page * G + g) * R + (e - (PAGE * (end / PAGE)) / P);
+          val = c < dk ? pk[rowi * dk + c] : pv[rowi * dv + (c - dk)];
+        }
+      }
+      if (c < dk) Ks[j * ks + c] = val; else Vs[j * dv + (c - dk)] = val;
+    }
+    __syncthreads();
+    process(e0, zero, top, valid);
+  }
+  // 2. the window's pages: from the page of the first row's first key to the page of the last row's position
+  const int kt_begin = max(0, first_pos - window + 1) / PAGE, kt_end = last_pos / PAGE;
+  for (int kt = kt_begin; kt <= kt_end; ++kt) {
+    const int page = pages[kt];
+    const bool held = page >= 0 && page < n_pages;
+    const T* kp = kcache + ((size_t)(held ? page : 0) * G + g) * PAGE * dk;
+    const T* vp = vcache + ((size_t)(held ? page : 0) * G + g) * PAGE * dv;
+    const int valid = held ? min(PAGE, last_pos + 1 - kt * PAGE) : 0;   // rows of the page that hold this block's keys
+    __syncthreads();
+    for (int i = threadIdx.x; i < PAGE * dk; i += blockDim.x) {
+      const int j = i / dk, d = i - j * dk;
+      Ks[j * ks + d] = j < valid ? to_f32(kp[i]) : 0.f;   // what lies behind is not this sequence's: never let it in
+    }
+    for (int i = threadIdx.x; i < PAGE * dv; i += blockDim.x) Vs[i] = i / dv < valid ? to_f32(vp[i]) : 0.f;
+    __syncthreads();
+    process(kt * PAGE, first, limit, valid);
+  }
+#pragma unroll
+  for (int r = 0; r < TW_RW; ++r) {
+    const int rr = row_base + warp * TW_RW + r;
+    if (rr >= rows_total) continue;
+    const int tok = rr / grp, head = g * grp + rr % grp;
+    const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dv) out[((size_t)(tok0 + tok) * H + head) * dv + d] = from_f32<T>(acc[r][c] * inv);
+    }
+  }
+}
+
 }  // namespace edgelm
 
 using namespace edgelm;
@@ -378,5 +545,48 @@ extern "C" int edgelm_pooled_window_attn(const void* q, void* out, const void* k
     EL_REFUSE(false, "pooled_window_attn: unknown dtype code %d", dtype);
 #undef EL_PWA
   EL_LAUNCH_CHECK("pooled_window_attn");
+  return 0;
+}
+
+// The same attention for prompt steps: tiles (runs of at most `max_tile_tokens` consecutive tokens of one sequence, as
+// the step's metadata lists them) instead of single tokens; `max_tile_tokens` x (H / G) rows are dealt to blocks of 32.
+template <typename T, int NC>
+static int launch_tiled(const void* q, void* out, const void* kc, const void* vc, const float* pk, const float* pv,
+                        const int32_t* page_table, int table_stride, int n_pages, const int32_t* tile_seq, const int32_t* tile_tok0,
+                        const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles, int max_tile_tokens, int H, int G, int dk, int dv,
+                        float scale, int window, int P, int R, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * ((size_t)TW_KEYS * (dk + 1) + (size_t)TW_KEYS * dv + (size_t)TW_ROWS * dk + (size_t)TW_ROWS * TW_KEYS);
+  auto kern = pooled_window_attn_tiled_kernel<T, NC>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    set_error("pooled_window_attn_tiled: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
+    return -2;
+  }
+  const dim3 grid(n_tiles, G, (max_tile_tokens * (H / G) + TW_ROWS - 1) / TW_ROWS);
+  kern<<<grid, TW_WARPS * 32, smem, stream>>>((const T*)q, (T*)out, (const T*)kc, (const T*)vc, pk, pv, page_table, table_stride, n_pages, tile_seq,
+                                             tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, window, P, R);
+  return 0;
+}
+
+extern "C" int edgelm_pooled_window_attn_tiled(const void* q, void* out, const void* kcache, const void* vcache, int dtype, const float* pk,
+                                               const float* pv, const int32_t* page_table, int table_stride, int n_pages,
+                                               const int32_t* tile_seq, const int32_t* tile_tok0, const int32_t* tile_ntok,
+                                               const int32_t* tile_pos0, int n_tiles, int max_tile_tokens, int H, int G, int dk, int dv,
+                                               float scale, int window, int P, int R, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  EL_REFUSE(n_tiles > 0 && max_tile_tokens > 0 && H > 0 && G > 0 && H % G == 0, "pooled_window_attn_tiled: %d query heads over %d key/value heads", H, G);
+  EL_REFUSE(dk >= 1 && dk <= 256 && dv >= 1 && dv <= 256, "pooled_window_attn_tiled: head sizes %d / %d are not taken (1 to 256)", dk, dv);
+  EL_REFUSE(window >= 1 && P >= 0 && (P == 0 || R == (PAGE + P - 1) / P), "pooled_window_attn_tiled: window %d, block %d, rows a page %d", window, P, R);
+  EL_REFUSE(dtype == DT_F32 || dtype == DT_BF16, "pooled_window_attn_tiled: unknown dtype code %d", dtype);
+  int rc;
+#define EL_TW(NC)                                                                                                                                  \
+  rc = dtype == DT_F32 ? launch_tiled<float, NC>(q, out, kcache, vcache, pk, pv, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, \
+                                                 tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, window, P, R, stream)                    \
+                       : launch_tiled<__nv_bfloat16, NC>(q, out, kcache, vcache, pk, pv, page_table, table_stride, n_pages, tile_seq, tile_tok0,   \
+                                                         tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, window, P, R, stream)
+  if (dv <= 32) { EL_TW(1); } else if (dv <= 64) { EL_TW(2); } else if (dv <= 128) { EL_TW(4); } else { EL_TW(8); }
+#undef EL_TW
+  if (rc != 0) return rc;
+  EL_LAUNCH_CHECK("pooled_window_attn_tiled");
   return 0;
 }

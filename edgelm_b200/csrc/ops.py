@@ -606,3 +606,24 @@ def pooled_window_attn(q, out, kcache, vcache, pooled_k, pooled_v, tok_pos, tok_
     _check(lib().edgelm_pooled_window_attn(_p(q), _p(out), _p(kcache), _p(vcache), _dt(q), _p(pooled_k) if pool else _p(None),
                                            _p(pooled_v) if pool else _p(None), _p(tok_pos), _p(tok_seq), _p(page_table), page_table.stride(0),
                                            kcache.shape[0], T, nh, nkv, dk, dv, ctypes.c_float(scale), int(window), int(pool or 0), rows, _stream()))
+
+
+def pooled_window_attn_tiled(q, out, kcache, vcache, pooled_k, pooled_v, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles,
+                             max_tile_tokens, nh, nkv, dk, dv, scale, window, pool):
+    """`pooled_window_attn` for prompt steps: the step's tokens come as tiles (runs of at most `max_tile_tokens` consecutive
+    tokens of one sequence: `tile_seq` the row of the page table, `tile_tok0` the first packed row, `tile_ntok`, `tile_pos0`
+    the first position); a page of keys and values is staged once for all the rows of a tile."""
+    T = q.shape[0]
+    _need(q.is_contiguous() and out.is_contiguous() and q.shape == (T, nh * dk) and out.shape == (T, nh * dv) and q.dtype == out.dtype == kcache.dtype, "pooled_window_attn_tiled: shapes")
+    _pooled_cache_check(kcache, vcache, nkv, dk, dv, "pooled_window_attn_tiled")
+    for t, n in ((page_table, "page_table"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
+        _i32(t, n)
+    rows = 0
+    if pool:
+        _f32(pooled_k, "pooled_k"); _f32(pooled_v, "pooled_v")
+        rows = pooled_k.shape[2]
+        _need(tuple(pooled_k.shape) == (kcache.shape[0], nkv, rows, dk) and tuple(pooled_v.shape) == (kcache.shape[0], nkv, rows, dv), "pooled_window_attn_tiled: pooled layout")
+    _check(lib().edgelm_pooled_window_attn_tiled(_p(q), _p(out), _p(kcache), _p(vcache), _dt(q), _p(pooled_k) if pool else _p(None),
+                                                 _p(pooled_v) if pool else _p(None), _p(page_table), page_table.stride(0), kcache.shape[0],
+                                                 _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles), int(max_tile_tokens),
+                                                 nh, nkv, dk, dv, ctypes.c_float(scale), int(window), int(pool or 0), rows, _stream()))

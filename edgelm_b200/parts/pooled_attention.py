@@ -45,6 +45,10 @@ class PooledWindowAttention(Part):
             raise ConfigError(f"pooled_window_attention: a window of {self.window} keys, blocks of {self.pool}")
         self.d_qkv = (self.nh + self.nkv) * self.dk + self.nkv * self.dv
         self.freq = self.b_qkv = None
+        self.tile_tokens = max(1, 32 // (self.nh // self.nkv))   # tokens whose heads fill one block of the prompt kernel
+
+    def tile_sizes(self):
+        return (self.tile_tokens,)
 
     def sizes(self):
         return {"heads": self.nh, "kv_heads": self.nkv, "head_dim": self.dk, "v_head_dim": self.dv, "window": self.window,
@@ -102,9 +106,15 @@ class PooledWindowAttention(Part):
                 ops.pool_blocks(ctx.tok_pos, ctx.tok_seq, table, cache.k, cache.v, cache.pooled_k, cache.pooled_v, T, self.nkv, self.dk,
                                 self.dv, self.pool, ctx.err)
         a = ws.alloc((T, self.nh * self.dv), self.dtype)
+        pooled_k, pooled_v = (cache.pooled_k, cache.pooled_v) if self.pool else (None, None)
         with ctx.prof("attn_window_pooled"):
-            ops.pooled_window_attn(q, a, cache.k, cache.v, cache.pooled_k if self.pool else None, cache.pooled_v if self.pool else None,
-                                   ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk, self.dv, self.scale, self.window, self.pool)
+            if ctx.all_single:      # one token a sequence: a block per (token, head), its warps sharing the keys
+                ops.pooled_window_attn(q, a, cache.k, cache.v, pooled_k, pooled_v, ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk,
+                                       self.dv, self.scale, self.window, self.pool)
+            else:                   # a prompt step: keys staged once for the 32 rows of a tile
+                tiles = ctx.tiles(self.tile_tokens)
+                ops.pooled_window_attn_tiled(q, a, cache.k, cache.v, pooled_k, pooled_v, table, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0,
+                                             tiles.count, self.tile_tokens, self.nh, self.nkv, self.dk, self.dv, self.scale, self.window, self.pool)
         with ctx.prof("o_proj"):
             linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
                           residual=x if accumulate else None, prefetch=ctx.weights_after)

@@ -182,6 +182,7 @@ def test_window_attention_with_pooled_blocks(dtype, window, pool, dk, dv, H, G):
     table = i32([[5, 2, 7, -1], [0, 6, -1, -1]])
     err = torch.zeros(1, dtype=torch.int32, device=DEV)
     got = [np.zeros_like(w) for w in want]
+    got_tiled = [np.zeros_like(w) for w in want]
     for step in steps_of(total, cuts):
         live = [(s, a, n) for s, (a, n) in enumerate(step) if n]
         T = sum(n for _, _, n in live)
@@ -193,15 +194,25 @@ def test_window_attention_with_pooled_blocks(dtype, window, pool, dk, dv, H, G):
         ops.pool_blocks(tok_pos, tok_seq, table, kc, vc, pk, pv, T, G, dk, dv, pool, err)
         out = torch.full((T, H * dv), float("nan"), dtype=dtype, device=DEV)
         ops.pooled_window_attn(qd, out, kc, vc, pk, pv, tok_pos, tok_seq, table, H, G, dk, dv, scale, window, pool)
-        out = out.float().cpu().numpy()
+        # the prompt kernel on the same step: runs of at most 32 / (H / G) tokens, 32 rows a block
+        from edgelm_b200.engine.batch import make_tiles
+        tile_tokens = max(1, 32 // (H // G))
+        assert [s for s, _, _ in live] == list(range(len(live)))      # (a tile's sequence index is its row of the page table)
+        cols = make_tiles([n for _, _, n in live], [a for _, a, _ in live], tile_tokens)
+        out_t = torch.full((T, H * dv), float("nan"), dtype=dtype, device=DEV)
+        ops.pooled_window_attn_tiled(qd, out_t, kc, vc, pk, pv, table, i32(cols[0]), i32(cols[1]), i32(cols[2]), i32(cols[3]), len(cols[0]),
+                                     tile_tokens, H, G, dk, dv, scale, window, pool)
+        out, out_t = out.float().cpu().numpy(), out_t.float().cpu().numpy()
         at = 0
         for s, a, n in live:
             got[s][a:a + n] = out[at:at + n]
+            got_tiled[s][a:a + n] = out_t[at:at + n]
             at += n
     assert int(err.item()) == 0
     tol = 2e-5 if dtype == torch.float32 else 2e-2
-    for w, o in zip(want, got):
+    for w, o, ot in zip(want, got, got_tiled):
         assert np.isfinite(o).all() and np.abs(o - w).max() < tol * max(1.0, np.abs(w).max())
+        assert np.isfinite(ot).all() and np.abs(ot - w).max() < tol * max(1.0, np.abs(w).max())
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
