@@ -141,7 +141,7 @@ class SagizenConfig:
                 ranks[i] = int(shapes[name][0])
         return self.with_decay_ranks(ranks) if ranks else self
 
-    DEFAULT_DECAY_RANK = 16
+    DEFAULT_DECAY_RANK = 32     # (used only where neither the configuration nor a stored tensor gives it: a plan without weights)
 
     def plan(self) -> ModelPlan:
         layers = tuple(self._layer(i, l, coerce(l.get("decay_rank", self.DEFAULT_DECAY_RANK), "decay_rank", int) if isinstance(l, Mapping) else 0)

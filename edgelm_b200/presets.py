@@ -15,9 +15,9 @@ def _sagizen(vocab, width, ff, groups_of_layers, ssm_heads, ssm_state, heads, kv
     dense = {"kind": "dense", "ff": ff}
     ssm = {"type": "mamba2", "mlp": dense,
            "mixer": {"heads": ssm_heads, "vdim": 64, "state": ssm_state, "groups": 1, "conv": 4, "norm_groups": 1}}
-    par = {"type": "parallel", "mlp": dense, "mixer": {
+    par = {"type": "parallel", "mlp": dense, "decay_rank": 64, "mixer": {
         "left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "mask": {"size": window, "pool": pool},
-                 "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 1.0}}, "scale": 0.125},
+                 "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 1.0}}, "scale": 0.125},
         "left_scale": 1.0, "right": {"heads": heads, "dim": 64}, "right_scale": 1.0}}
     return {"architecture": "Sagizen", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "max_positions": 8192,
             "layers": [ssm, ssm, ssm, par] * groups_of_layers}

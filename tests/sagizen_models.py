@@ -41,7 +41,7 @@ CFG_B = {"architecture": "Sagizen", "vocab": 97, "width": 50, "norm": {"eps": 3e
     mamba(2, 24, 8, 2, 1, 2, 30),
     parallel(2, 2, 32, 32, 33, 5, None, 0.2, 1, 40, 0.9, 1.1, 64),
 ]}
-DECAY_RANK = {"a": 16, "b": 5}     # the rank of the decay's projection is a size that only the tensors' shapes give
+DECAY_RANK = {"a": 24, "b": 5}     # the rank of the decay's projection is a size that only the tensors' shapes give
 CONFIGS = {"a": CFG_A, "b": CFG_B}
 
 
@@ -100,7 +100,7 @@ def tensors_for(cfg, seed, decay_rank):
     return W
 
 
-def write_dir(path, cfg, seed, decay_rank=16, overrides=None):
+def write_dir(path, cfg, seed, decay_rank=24, overrides=None):
     """config.json and model.safetensors (bfloat16) for `cfg`; `overrides`: name -> array put in place of the drawn one."""
     from edgelm_b200.weights import write_file
     os.makedirs(path, exist_ok=True)
