@@ -45,7 +45,7 @@ class CacheEntry:
 
     @property
     def v(self):
-        return self.group.v[self.index]
+        return self.group.v[self.index] if self.group.v is not None else None
 
     @property
     def state(self):
@@ -101,13 +101,14 @@ class KVGroup:
         self.pooled_rows = -(-PAGE // self.pool_block) if self.pool_block else 0     # block ends that fall into one page, at most
         if device is not None:
             self.k = torch.zeros((n_entries, n_pages, need.n_kv_heads, PAGE, need.head_dim), dtype=dtype, device=device)
-            self.v = torch.zeros((n_entries, n_pages, need.n_kv_heads, PAGE, self.v_head_dim), dtype=dtype, device=device)
+            if not need.values_in_keys:
+                self.v = torch.zeros((n_entries, n_pages, need.n_kv_heads, PAGE, self.v_head_dim), dtype=dtype, device=device)
             if self.pool_block:
                 self.pooled_k = torch.zeros((n_entries, n_pages, need.n_kv_heads, self.pooled_rows, need.head_dim), dtype=torch.float32, device=device)
                 self.pooled_v = torch.zeros((n_entries, n_pages, need.n_kv_heads, self.pooled_rows, self.v_head_dim), dtype=torch.float32, device=device)
 
     def bytes_per_token(self, itemsize):
-        per_row = self.need.head_dim + self.v_head_dim
+        per_row = self.need.head_dim + (0 if self.need.values_in_keys else self.v_head_dim)
         pooled = self.pooled_rows * per_row * 4 / PAGE
         return int(self.n_entries * self.need.n_kv_heads * (per_row * itemsize + pooled))
 

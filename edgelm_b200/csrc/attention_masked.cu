@@ -1,0 +1,601 @@
+// Attention over the paged cache with a key range per query and an optional sink, for head sizes that the other
+// attention kernels do not take, and the kernels that prepare its queries and keys.
+//
+// A query at position i sees the keys lo(i) .. i, where lo depends on the mask:
+//   MASK_CAUSAL  lo = 0
+//   MASK_WINDOW  lo = max(0, i - size + 1)                  (the last `size` keys)
+//   MASK_CHUNK   lo = (i / size) * size                     (the keys of its own chunk of `size` positions)
+// `sink` (optional, one float per query head): one more term exp(sink_h) in the softmax's denominator that has no key
+// and no value and is not scaled.  Scores, maxima, exponentials, sums and weighted values are float32; queries come
+// as float32, keys and values in the cache's type.
+//
+// Cache layout: keys [page][kv_head][PAGE][dk]; values either [page][kv_head][PAGE][dv] (a tensor of their own) or
+// the first dv dimensions of each key row (`vcache` null: a latent that is key and value at once).
+//
+// Kernels: `rotate_append` (bias, rotation of a part of every query and key head with neighbouring or half-split
+// pairs, cache append); `latent_prepare` (rotation of the queries' rotated part; RMS norm of the latent, rotation of
+// the shared key part, cache append); `head_matmul` (one small matrix product per head: queries into the latent's
+// space, weighted latents out of it); `masked_attn` (a block per token and head: steps of one token a sequence);
+// `masked_attn_tiled` (prompt steps: keys staged once for 32 rows); `add_row_bias`.
+#include "common.cuh"
+
+namespace edgelm {
+
+enum : int { MASK_CAUSAL = 0, MASK_WINDOW = 1, MASK_CHUNK = 2 };
+
+__device__ __forceinline__ int first_key(int pos, int mask, int size) {
+  if (mask == MASK_WINDOW) return max(0, pos - size + 1);
+  if (mask == MASK_CHUNK) return (pos / size) * size;
+  return 0;
+}
+
+// sine and cosine of position * f: the product is formed in float64 and brought into [-pi, pi] before it is rounded
+// (a float32 product alone is off by 3e-5 rad at position 1,000)
+__device__ __forceinline__ void angle_sincos(double pos, double f, float* sn, float* cs) {
+  double a = pos * f;
+  a -= 6.283185307179586477 * rint(a * 0.15915494309189533577);
+  sincosf((float)a, sn, cs);
+}
+
+// element i (< rot) of a rotated run x[0 .. rot): pairs (2j, 2j + 1) if `interleaved`, else (j, j + rot / 2)
+__device__ __forceinline__ float rotated(const float* x, int i, int rot, int interleaved, double pos, const double* __restrict__ freq) {
+  const int half = rot >> 1;
+  int j, partner;
+  bool first;
+  if (interleaved) { j = i >> 1; first = (i & 1) == 0; partner = i ^ 1; }
+  else { first = i < half; j = first ? i : i - half; partner = first ? i + half : i - half; }
+  float sn, cs;
+  angle_sincos(pos, freq[j], &sn, &cs);
+  return first ? x[i] * cs - x[partner] * sn : x[i] * cs + x[partner] * sn;
+}
+
+constexpr int MA_WARPS = 4;
+
+// qkv [tokens][H dk + G dk + G dv] float32 (+ bias): the first `rot` dimensions of every query and key head rotated;
+// queries to q_out [tokens][H][dk] float32, keys and values into their cache rows.
+template <typename T>
+__global__ void __launch_bounds__(MA_WARPS * 32)
+rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bias, float* __restrict__ q_out,
+                     const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
+                     int table_stride, int n_pages, T* __restrict__ kcache, T* __restrict__ vcache, int H, int G, int dk, int dv,
+                     int rot, int interleaved, const double* __restrict__ freq, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float ra_stage[];   // MA_WARPS rows of dk floats
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = tok_pos[t];
+  if (pos < 0) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, ERR_POSITION_RANGE);
+    return;
+  }
+  const int page = page_table[(size_t)tok_seq[t] * table_stride + pos / PAGE];
+  if (page < 0 || page >= n_pages) {
+    if (threadIdx.x == 0 && blockIdx.y == 0) atomicOr(err, ERR_PAGE_RANGE);
+    return;
+  }
+  const int in_page = pos % PAGE;
+  const int ld = H * dk + G * dk + G * dv;
+  const float* row = qkv + (size_t)t * ld;
+  float* sh = ra_stage + warp * dk;
+  for (int head = blockIdx.y * MA_WARPS + warp; head < H + G; head += gridDim.y * MA_WARPS) {
+    const float* src = row + (size_t)head * dk;
+    const float* b = bias ? bias + (size_t)head * dk : nullptr;
+    for (int i = lane; i < dk; i += 32) sh[i] = src[i] + (b ? b[i] : 0.f);
+    __syncwarp();
+    for (int i = lane; i < dk; i += 32) {
+      const float x = i < rot ? rotated(sh, i, rot, interleaved, (double)pos, freq) : sh[i];
+      if (head < H) q_out[((size_t)t * H + head) * dk + i] = x;
+      else kcache[(((size_t)page * G + (head - H)) * PAGE + in_page) * dk + i] = from_f32<T>(x);
+    }
+    __syncwarp();
+  }
+  const float* vrow = row + (size_t)(H + G) * dk;
+  const float* vb = bias ? bias + (size_t)(H + G) * dk : nullptr;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < G * dv; i += gridDim.y * blockDim.x) {
+    const int g = i / dv, j = i - g * dv;
+    vcache[(((size_t)page * G + g) * PAGE + in_page) * dv + j] = from_f32<T>(vrow[i] + (vb ? vb[i] : 0.f));
+  }
+}
+
+// u [tokens][ldu] float32: H query heads of [d | rd] from column 0 and, with `has_kv`, the latent's row [r | rd] from
+// column kv_off.  The rotated part of every query head (half-split pairs) goes to q_full[t][h][r + i]; the latent,
+// divided by its root mean square and times `norm_w`, and the rotated shared key part become the token's cache row
+// [r + rd] (one key head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+latent_prepare_kernel(const float* __restrict__ u, int ldu, int kv_off, int has_kv, float* __restrict__ q_full,
+                      const float* __restrict__ norm_w, float eps, const int32_t* __restrict__ tok_pos,
+                      const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table, int table_stride, int n_pages,
+                      T* __restrict__ kcache, int H, int d, int rd, int r, const double* __restrict__ freq, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int pos = tok_pos[t];
+  if (pos < 0) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_POSITION_RANGE);
+    return;
+  }
+  const float* row = u + (size_t)t * ldu;
+  for (int i = threadIdx.x; i < H * rd; i += blockDim.x) {
+    const int h = i / rd, j = i - h * rd;
+    q_full[((size_t)t * H + h) * (r + rd) + r + j] = rotated(row + (size_t)h * (d + rd) + d, j, rd, 0, (double)pos, freq);
+  }
+  if (!has_kv) return;
+  const int page = page_table[(size_t)tok_seq[t] * table_stride + pos / PAGE];
+  if (page < 0 || page >= n_pages) {
+    if (threadIdx.x == 0) atomicOr(err, ERR_PAGE_RANGE);
+    return;
+  }
+  const float* c = row + kv_off;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < r; i += blockDim.x) ss = fmaf(c[i], c[i], ss);
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)r + eps);
+  T* dst = kcache + ((size_t)page * PAGE + pos % PAGE) * (r + rd);
+  for (int i = threadIdx.x; i < r; i += blockDim.x) dst[i] = from_f32<T>(c[i] * inv * norm_w[i]);
+  for (int i = threadIdx.x; i < rd; i += blockDim.x) dst[r + i] = from_f32<T>(rotated(c + r, i, rd, 0, (double)pos, freq));
+}
+
+// out[t][h * out_hs + n] = sum_k a[t][h * a_hs + k] * w[h][n][k], float32 sums; a: float32 rows of lda floats, out: rows of ldo values.
+constexpr int HM_TT = 32, HM_TN = 64, HM_KC = 32;
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+head_matmul_kernel(const float* __restrict__ a, int lda, int a_hs, const TW* __restrict__ w, TO* __restrict__ out, int ldo,
+                   int out_hs, int n_tokens, int K, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float As[HM_TT][HM_KC + 1];
+  __shared__ float Ws[HM_TN][HM_KC + 1];
+  const int h = blockIdx.z, t0 = blockIdx.x * HM_TT, n0 = blockIdx.y * HM_TN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;     // 16 column groups of 4, 16 row groups of 2
+  const TW* wh = w + (size_t)h * N * K;
+  float acc[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += HM_KC) {
+    for (int i = threadIdx.x; i < HM_TT * HM_KC; i += 256) {
+      const int r = i / HM_KC, k = i - r * HM_KC;
+      As[r][k] = (t0 + r < n_tokens && k0 + k < K) ? a[(size_t)(t0 + r) * lda + (size_t)h * a_hs + k0 + k] : 0.f;
+    }
+    for (int i = threadIdx.x; i < HM_TN * HM_KC; i += 256) {
+      const int r = i / HM_KC, k = i - r * HM_KC;
+      Ws[r][k] = (n0 + r < N && k0 + k < K) ? to_f32(wh[(size_t)(n0 + r) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < HM_KC; ++k) {
+      const float a0 = As[ty * 2][k], a1 = As[ty * 2 + 1][k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float wv = Ws[tx + 16 * j][k];
+        acc[0][j] = fmaf(a0, wv, acc[0][j]);
+        acc[1][j] = fmaf(a1, wv, acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int t = t0 + ty * 2 + i, n = n0 + tx + 16 * j;
+      if (t < n_tokens && n < N) out[(size_t)t * ldo + (size_t)h * out_hs + n] = from_f32<TO>(acc[i][j]);
+    }
+}
+
+// x[t][:] += b[:]
+__global__ void add_row_bias_kernel(float* __restrict__ x, const float* __restrict__ b, int dim) {
+  pdl_launch_dependents();
+  pdl_wait();
+  float* row = x + (size_t)blockIdx.x * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) row[i] += b[i];
+}
+
+// q . k over n dimensions, q float32 in shared memory; four running sums
+__device__ __forceinline__ float ma_dot(const float* __restrict__ q, const float* __restrict__ k, int n, bool vec) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int i = 0;
+  if (vec)
+    for (; i + 4 <= n; i += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(k + i);
+      const float4 qv = *reinterpret_cast<const float4*>(q + i);
+      a0 = fmaf(qv.x, kv.x, a0); a1 = fmaf(qv.y, kv.y, a1); a2 = fmaf(qv.z, kv.z, a2); a3 = fmaf(qv.w, kv.w, a3);
+    }
+  for (; i < n; ++i) a0 = fmaf(q[i], k[i], a0);
+  return (a0 + a1) + (a2 + a3);
+}
+__device__ __forceinline__ float ma_dot(const float* __restrict__ q, const __nv_bfloat16* __restrict__ k, int n, bool vec) {
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  int i = 0;
+  if (vec)
+    for (; i + 8 <= n; i += 8) {
+      const uint4 kv = *reinterpret_cast<const uint4*>(k + i);
+      const float4 q0 = *reinterpret_cast<const float4*>(q + i), q1 = *reinterpret_cast<const float4*>(q + i + 4);
+      a0 = fmaf(q0.x, __uint_as_float(kv.x << 16), a0); a1 = fmaf(q0.y, __uint_as_float(kv.x & 0xffff0000u), a1);
+      a2 = fmaf(q0.z, __uint_as_float(kv.y << 16), a2); a3 = fmaf(q0.w, __uint_as_float(kv.y & 0xffff0000u), a3);
+      a0 = fmaf(q1.x, __uint_as_float(kv.z << 16), a0); a1 = fmaf(q1.y, __uint_as_float(kv.z & 0xffff0000u), a1);
+      a2 = fmaf(q1.z, __uint_as_float(kv.w << 16), a2); a3 = fmaf(q1.w, __uint_as_float(kv.w & 0xffff0000u), a3);
+    }
+  for (; i < n; ++i) a0 = fmaf(q[i], __bfloat162float(k[i]), a0);
+  return (a0 + a1) + (a2 + a3);
+}
+
+constexpr int MA_MAX_WARPS = 8;
+
+// A block per (token, query head); its warps take the visible keys in turns of 32 (a lane a key), each with its own
+// running maximum, denominator and weighted values, merged at the end through shared memory in a fixed order.
+// Dynamic shared memory: the scaled query (dk floats), then per warp its maximum, its denominator and dv values.
+// DVR: value dimensions a lane holds (d = lane + 32 r), so value heads of up to 32 DVR dimensions.
+template <typename T, typename TO, int DVR>
+__global__ void __launch_bounds__(MA_MAX_WARPS * 32)
+masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vbase, int ldv,
+                   const int32_t* __restrict__ tok_pos, const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table,
+                   int table_stride, int n_pages, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
+                   const float* __restrict__ sink, int vec_k) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) float ma_smem[];
+  const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
+  const int dkp = (dk + 3) & ~3;
+  float* qh = ma_smem;
+  float* wm = ma_smem + dkp;
+  float* wl = wm + NW;
+  float* wo = wl + NW;             // [NW][dv]
+  const int pos = tok_pos[t];
+  if (pos < 0) return;
+  const int g = h / (H / G);
+  const int32_t* table = page_table + (size_t)tok_seq[t] * table_stride;
+  const float* qrow = q + ((size_t)t * H + h) * dk;
+  for (int i = threadIdx.x; i < dk; i += blockDim.x) qh[i] = qrow[i] * scale;
+  __syncthreads();
+  const int lo = first_key(pos, mask, mask_size), n_keys = pos - lo + 1;
+  const int n_chunks = (n_keys + 31) >> 5;
+  float m = -INFINITY, l = 0.f;
+  float o[DVR];
+#pragma unroll
+  for (int r = 0; r < DVR; ++r) o[r] = 0.f;
+  for (int c = warp; c < n_chunks; c += NW) {
+    const int n_here = min(32, n_keys - c * 32);
+    float sc = -INFINITY;
+    int vrow = -1;
+    if (lane < n_here) {
+      const int p = lo + c * 32 + lane;
+      const int page = table[p / PAGE];
+      if (page >= 0 && page < n_pages) {
+        vrow = (page * G + g) * PAGE + p % PAGE;
+        sc = ma_dot(qh, kcache + (size_t)vrow * dk, dk, vec_k != 0);
+      }
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    if (m_new == -INFINITY) continue;
+    const float w = sc == -INFINITY ? 0.f : expf(sc - m_new);
+    const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
+    l = l * corr + warp_sum(w);
+    m = m_new;
+#pragma unroll
+    for (int r = 0; r < DVR; ++r) o[r] *= corr;
+#pragma unroll 4
+    for (int j = 0; j < n_here; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, w, j);
+      const int vr_i = __shfl_sync(0xffffffffu, vrow, j);
+      if (vr_i < 0) continue;
+      const T* vr = vbase + (size_t)vr_i * ldv;
+#pragma unroll
+      for (int r = 0; r < DVR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < dv) o[r] = fmaf(wj, to_f32(vr[d]), o[r]);
+      }
+    }
+  }
+  if (lane == 0) { wm[warp] = m; wl[warp] = l; }
+#pragma unroll
+  for (int r = 0; r < DVR; ++r) {
+    const int d = lane + 32 * r;
+    if (d < dv) wo[warp * dv + d] = o[r];
+  }
+  __syncthreads();
+  float M = sink ? sink[h] : -INFINITY;
+  for (int w2 = 0; w2 < NW; ++w2) M = fmaxf(M, wm[w2]);
+  float L = sink ? expf(sink[h] - M) : 0.f;
+  for (int w2 = 0; w2 < NW; ++w2) L += wm[w2] == -INFINITY ? 0.f : wl[w2] * expf(wm[w2] - M);
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int w2 = 0; w2 < NW; ++w2)
+      if (wm[w2] != -INFINITY) acc = fmaf(wo[w2 * dv + d], expf(wm[w2] - M), acc);
+    out[((size_t)t * H + h) * dv + d] = from_f32<TO>(acc * inv);
+  }
+}
+
+// ---- prompt steps
+// A block = up to 32 (token, query head) rows of one key/value head and of one run of consecutive tokens (a tile of the
+// step's metadata); a page of 64 keys with their values is staged in shared memory as float32 once for all the rows.
+// A warp owns four rows, so a key element read from shared memory serves four multiply-adds; lanes own keys for the
+// scores and value dimensions for the weighted sum.  Row r sees key p iff first[r] <= p <= its own position.
+constexpr int TM_RW = 4, TM_WARPS = 8, TM_ROWS = TM_RW * TM_WARPS, TM_KEYS = PAGE;
+
+template <typename T, typename TO, int NC>    // NC = ceil(dv / 32): value dimensions a lane owns
+__global__ void __launch_bounds__(TM_WARPS * 32)
+masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
+                         const int32_t* __restrict__ page_table, int table_stride, int n_pages, const int32_t* __restrict__ tile_seq,
+                         const int32_t* __restrict__ tile_tok0, const int32_t* __restrict__ tile_ntok, const int32_t* __restrict__ tile_pos0,
+                         int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* __restrict__ sink) {
+  extern __shared__ float tm_smem[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int ks = dk + 1;                        // padded key row: lanes read different rows
+  const bool own_v = vcache != nullptr;
+  const int vs = own_v ? dv : ks;               // a staged value row's pitch (values inside the keys: the key's)
+  float* Ks = tm_smem;                          // [TM_KEYS][dk + 1]
+  float* Vs = own_v ? Ks + TM_KEYS * ks : Ks;   // [TM_KEYS][dv]
+  float* Qs = Ks + TM_KEYS * ks + (own_v ? TM_KEYS * dv : 0);   // [TM_ROWS][dk]
+  float* Ps = Qs + TM_ROWS * dk;                // [TM_ROWS][TM_KEYS]
+  const int tile = blockIdx.x, g = blockIdx.y, grp = H / G;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int seq = tile_seq[tile], tok0 = tile_tok0[tile], ntok = tile_ntok[tile], pos0 = tile_pos0[tile];
+  const int32_t* pages = page_table + (size_t)seq * table_stride;
+  const int rows_total = ntok * grp, row_base = blockIdx.z * TM_ROWS;
+  if (row_base >= rows_total) return;
+  const int rows_here = min(TM_ROWS, rows_total - row_base);
+  const int last_pos = pos0 + (row_base + rows_here - 1) / grp, first_pos = pos0 + row_base / grp;
+  for (int i = threadIdx.x; i < TM_ROWS * dk; i += blockDim.x) {
+    const int r = i / dk, d = i - r * dk;
+    const int rr = row_base + r, tok = rr / grp, head = g * grp + rr % grp;
+    Qs[i] = r < rows_here ? q[((size_t)(tok0 + tok) * H + head) * dk + d] : 0.f;
+  }
+  float m[TM_RW], l[TM_RW], acc[TM_RW][NC];
+  int limit[TM_RW], first[TM_RW];
+#pragma unroll
+  for (int r = 0; r < TM_RW; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+    const int rr = row_base + warp * TM_RW + r;
+    limit[r] = rr < rows_total ? pos0 + rr / grp : -1;                       // the row's own position; -1: no row
+    first[r] = limit[r] < 0 ? 0 : first_key(limit[r], mask, mask_size);
+#pragma unroll
+    for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
+  }
+  const int kt_begin = first_key(first_pos, mask, mask_size) / PAGE, kt_end = last_pos / PAGE;
+  for (int kt = kt_begin; kt <= kt_end; ++kt) {
+    const int page = pages[kt];
+    const bool held = page >= 0 && page < n_pages;
+    const T* kp = kcache + ((size_t)(held ? page : 0) * G + g) * PAGE * dk;
+    const int valid = held ? min(PAGE, last_pos + 1 - kt * PAGE) : 0;   // rows of the page that hold this block's keys
+    __syncthreads();
+    for (int i = threadIdx.x; i < PAGE * dk; i += blockDim.x) {
+      const int j = i / dk, d = i - j * dk;
+      Ks[j * ks + d] = j < valid ? to_f32(kp[i]) : 0.f;   // what lies behind is not this sequence's: never let it in
+    }
+    if (own_v) {
+      const T* vp = vcache + ((size_t)(held ? page : 0) * G + g) * PAGE * dv;
+      for (int i = threadIdx.x; i < PAGE * dv; i += blockDim.x) Vs[i] = i / dv < valid ? to_f32(vp[i]) : 0.f;
+    }
+    __syncthreads();
+    const int base = kt * PAGE;
+    int any_hi = -1, any_lo = 0x7fffffff;
+#pragma unroll
+    for (int r = 0; r < TM_RW; ++r)
+      if (limit[r] >= first[r]) { any_hi = max(any_hi, limit[r]); any_lo = min(any_lo, first[r]); }
+    if (base > any_hi || base + TM_KEYS - 1 < any_lo) continue;     // none of this warp's rows sees any of these keys
+    const int i0 = base + lane, i1 = i0 + 32;
+    float s0[TM_RW] = {}, s1[TM_RW] = {};
+    const float* k0 = Ks + lane * ks;
+    const float* k1 = Ks + (lane + 32) * ks;
+    const float* qw = Qs + warp * TM_RW * dk;
+    for (int d = 0; d < dk; ++d) {
+      const float a = k0[d], b = k1[d];
+#pragma unroll
+      for (int r = 0; r < TM_RW; ++r) {
+        const float qv = qw[r * dk + d];
+        s0[r] = fmaf(qv, a, s0[r]);
+        s1[r] = fmaf(qv, b, s1[r]);
+      }
+    }
+    float corr[TM_RW];
+#pragma unroll
+    for (int r = 0; r < TM_RW; ++r) {
+      const float a = i0 >= first[r] && i0 <= limit[r] ? s0[r] * scale : -INFINITY;
+      const float b = i1 >= first[r] && i1 <= limit[r] ? s1[r] * scale : -INFINITY;
+      const float mx = fmaxf(m[r], warp_max(fmaxf(a, b)));
+      float p0 = 0.f, p1 = 0.f;
+      corr[r] = 1.f;
+      if (mx != -INFINITY) {      // uniform over the warp
+        corr[r] = expf(m[r] - mx);
+        p0 = expf(a - mx);
+        p1 = expf(b - mx);
+        l[r] = l[r] * corr[r] + warp_sum(p0 + p1);
+        m[r] = mx;
+      }
+      Ps[(warp * TM_RW + r) * TM_KEYS + lane] = p0;
+      Ps[(warp * TM_RW + r) * TM_KEYS + lane + 32] = p1;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < TM_RW; ++r)
+#pragma unroll
+      for (int c = 0; c < NC; ++c) acc[r][c] *= corr[r];
+    const float* pw = Ps + warp * TM_RW * TM_KEYS;
+    for (int j = 0; j < valid; ++j) {
+      float v[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int d = lane + 32 * c;
+        v[c] = d < dv ? Vs[j * vs + d] : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < TM_RW; ++r) {
+        const float pj = pw[r * TM_KEYS + j];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) acc[r][c] = fmaf(pj, v[c], acc[r][c]);
+      }
+    }
+    __syncwarp();
+  }
+#pragma unroll
+  for (int r = 0; r < TM_RW; ++r) {
+    const int rr = row_base + warp * TM_RW + r;
+    if (rr >= rows_total) continue;
+    const int tok = rr / grp, head = g * grp + rr % grp;
+    float lr = l[r], fix = 1.f;
+    if (sink) {                                   // the sink: one more term of the denominator, no value
+      const float sk = sink[head], mx = fmaxf(m[r], sk);
+      fix = m[r] == -INFINITY ? 0.f : expf(m[r] - mx);
+      lr = lr * fix + expf(sk - mx);
+    }
+    const float inv = lr > 0.f ? fix / lr : 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      const int d = lane + 32 * c;
+      if (d < dv) out[((size_t)(tok0 + tok) * H + head) * dv + d] = from_f32<TO>(acc[r][c] * inv);
+    }
+  }
+}
+
+}  // namespace edgelm
+
+using namespace edgelm;
+
+extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* q_out, const int32_t* tok_pos, const int32_t* tok_seq,
+                                    const int32_t* page_table, int table_stride, int n_pages, void* kcache, void* vcache, int dtype,
+                                    int n_tokens, int H, int G, int dk, int dv, int rot, int interleaved, const double* freq, int* err,
+                                    cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && H > 0 && G > 0 && H % G == 0, "rotate_append: %d query heads over %d key/value heads", H, G);
+  EL_REFUSE(dk >= 1 && dk <= 2048 && dv >= 1, "rotate_append: head sizes %d / %d are not taken", dk, dv);
+  EL_REFUSE(rot >= 0 && rot <= dk && rot % 2 == 0 && (rot == 0 || freq != nullptr), "rotate_append: %d rotated dimensions of %d", rot, dk);
+  const size_t smem = (size_t)MA_WARPS * dk * sizeof(float);
+  const dim3 grid(n_tokens, (H + G + MA_WARPS - 1) / MA_WARPS), block(MA_WARPS * 32);
+  const int bit = pdl_bit_for_tokens(n_tokens);
+  if (dtype == DT_F32)
+    launch_pdl(bit, rotate_append_kernel<float>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table, table_stride,
+               n_pages, (float*)kcache, (float*)vcache, H, G, dk, dv, rot, interleaved, freq, err);
+  else if (dtype == DT_BF16)
+    launch_pdl(bit, rotate_append_kernel<__nv_bfloat16>, grid, block, smem, stream, qkv, bias, q_out, tok_pos, tok_seq, page_table,
+               table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, H, G, dk, dv, rot, interleaved, freq, err);
+  else
+    EL_REFUSE(false, "rotate_append: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("rotate_append");
+  return 0;
+}
+
+extern "C" int edgelm_latent_prepare(const float* u, int ldu, int kv_off, int has_kv, float* q_full, const float* norm_w, float eps,
+                                     const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table, int table_stride,
+                                     int n_pages, void* kcache, int dtype, int n_tokens, int H, int d, int rd, int r, const double* freq,
+                                     int* err, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && H > 0 && d >= 0 && r >= 1 && rd >= 0 && rd % 2 == 0, "latent_prepare: sizes heads %d, %d + %d, latent %d", H, d, rd, r);
+  EL_REFUSE(rd == 0 || freq != nullptr, "latent_prepare: no frequencies");
+  EL_REFUSE(H * (d + rd) <= ldu && (!has_kv || kv_off + r + rd <= ldu), "latent_prepare: rows of %d values are too short", ldu);
+  const int bit = pdl_bit_for_tokens(n_tokens);
+  if (dtype == DT_F32)
+    launch_pdl(bit, latent_prepare_kernel<float>, dim3(n_tokens), dim3(256), (size_t)0, stream, u, ldu, kv_off, has_kv, q_full, norm_w, eps,
+               tok_pos, tok_seq, page_table, table_stride, n_pages, (float*)kcache, H, d, rd, r, freq, err);
+  else if (dtype == DT_BF16)
+    launch_pdl(bit, latent_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), (size_t)0, stream, u, ldu, kv_off, has_kv, q_full, norm_w,
+               eps, tok_pos, tok_seq, page_table, table_stride, n_pages, (__nv_bfloat16*)kcache, H, d, rd, r, freq, err);
+  else
+    EL_REFUSE(false, "latent_prepare: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("latent_prepare");
+  return 0;
+}
+
+extern "C" int edgelm_head_matmul(const float* a, int lda, int a_hs, const void* w, int w_dtype, void* out, int out_dtype, int ldo, int out_hs,
+                                  int n_tokens, int H, int K, int N, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && H > 0 && K > 0 && N > 0 && H <= 65535, "head_matmul: bad sizes heads %d, K %d, N %d", H, K, N);
+  const dim3 grid((n_tokens + HM_TT - 1) / HM_TT, (N + HM_TN - 1) / HM_TN, H), block(256);
+  const int bit = pdl_bit_for_tokens(n_tokens);
+#define EL_HM(TW, TO) launch_pdl(bit, head_matmul_kernel<TW, TO>, grid, block, (size_t)0, stream, a, lda, a_hs, (const TW*)w, (TO*)out, ldo, out_hs, n_tokens, K, N)
+  if (w_dtype == DT_F32 && out_dtype == DT_F32) EL_HM(float, float);
+  else if (w_dtype == DT_BF16 && out_dtype == DT_F32) EL_HM(__nv_bfloat16, float);
+  else if (w_dtype == DT_BF16 && out_dtype == DT_BF16) EL_HM(__nv_bfloat16, __nv_bfloat16);
+  else EL_REFUSE(false, "head_matmul: dtype codes %d -> %d are not taken", w_dtype, out_dtype);
+#undef EL_HM
+  EL_LAUNCH_CHECK("head_matmul");
+  return 0;
+}
+
+extern "C" int edgelm_add_row_bias(float* x, const float* b, int n_tokens, int dim, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && dim > 0, "add_row_bias: bad sizes");
+  launch_pdl(pdl_bit_for_tokens(n_tokens), add_row_bias_kernel, dim3(n_tokens), dim3(dim >= 1024 ? 256 : 128), (size_t)0, stream, x, b, dim);
+  EL_LAUNCH_CHECK("add_row_bias");
+  return 0;
+}
+
+static int masked_common_check(const char* what, int H, int G, int dk, int dv, int mask, int mask_size, int dtype, int out_dtype) {
+  EL_REFUSE(H > 0 && G > 0 && H % G == 0, "%s: %d query heads over %d key/value heads", what, H, G);
+  EL_REFUSE(dk >= 1 && dk <= 1024 && dv >= 1 && dv <= 512, "%s: head sizes %d / %d are not taken (keys to 1024, values to 512)", what, dk, dv);
+  EL_REFUSE(mask == MASK_CAUSAL || ((mask == MASK_WINDOW || mask == MASK_CHUNK) && mask_size >= 1), "%s: mask %d of size %d", what, mask, mask_size);
+  EL_REFUSE((dtype == DT_F32 && out_dtype == DT_F32) || (dtype == DT_BF16 && (out_dtype == DT_F32 || out_dtype == DT_BF16)),
+            "%s: dtype codes %d -> %d are not taken", what, dtype, out_dtype);
+  return 0;
+}
+
+template <typename T, typename TO, int DVR>
+static void launch_masked(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* tok_pos, const int32_t* tok_seq,
+                          const int32_t* page_table, int table_stride, int n_pages, int n_tokens, int H, int G, int dk, int dv, float scale,
+                          int mask, int mask_size, const float* sink, int warps, cudaStream_t stream) {
+  const T* vb = vcache ? (const T*)vcache : (const T*)kcache;
+  const int ldv = vcache ? dv : dk;
+  const int vec_k = (dk % (16 / (int)sizeof(T)) == 0) && ((uintptr_t)kcache % 16 == 0);
+  const size_t smem = ((size_t)((dk + 3) & ~3) + (size_t)warps * (2 + dv)) * sizeof(float);
+  auto kern = masked_attn_kernel<T, TO, DVR>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  launch_pdl(pdl_bit_for_tokens(n_tokens), kern, dim3(n_tokens, H), dim3(warps * 32), smem, stream, q, (TO*)out, (const T*)kcache, vb, ldv,
+             tok_pos, tok_seq, page_table, table_stride, n_pages, H, G, dk, dv, scale, mask, mask_size, sink, vec_k);
+}
+
+// `vcache` null: the values are the first dv dimensions of the key rows.  `max_keys`: the most keys a token of the step sees
+// (chooses how many warps share a token's keys).
+extern "C" int edgelm_masked_attn(const float* q, void* out, int out_dtype, const void* kcache, const void* vcache, int dtype,
+                                  const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table, int table_stride, int n_pages,
+                                  int n_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* sink,
+                                  int max_keys, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  if (masked_common_check("masked_attn", H, G, dk, dv, mask, mask_size, dtype, out_dtype)) return -1;
+  EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn: values of %d inside keys of %d", dv, dk);
+  const int warps = max_keys <= 64 ? 2 : (max_keys <= 256 ? 4 : MA_MAX_WARPS);
+#define EL_MA2(T, TO, DVR) launch_masked<T, TO, DVR>(q, out, kcache, vcache, tok_pos, tok_seq, page_table, table_stride, n_pages, n_tokens, H, G, dk, dv, scale, mask, mask_size, sink, warps, stream)
+#define EL_MA(DVR) do { if (dtype == DT_F32) EL_MA2(float, float, DVR); else if (out_dtype == DT_F32) EL_MA2(__nv_bfloat16, float, DVR); else EL_MA2(__nv_bfloat16, __nv_bfloat16, DVR); } while (0)
+  if (dv <= 32) EL_MA(1); else if (dv <= 64) EL_MA(2); else if (dv <= 128) EL_MA(4); else if (dv <= 256) EL_MA(8); else EL_MA(16);
+#undef EL_MA
+#undef EL_MA2
+  EL_LAUNCH_CHECK("masked_attn");
+  return 0;
+}
+
+template <typename T, typename TO, int NC>
+static int launch_masked_tiled(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* page_table, int table_stride,
+                               int n_pages, const int32_t* tile_seq, const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0,
+                               int n_tiles, int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
+                               const float* sink, cudaStream_t stream) {
+  const size_t smem = ((size_t)TM_KEYS * (dk + 1) + (vcache ? (size_t)TM_KEYS * dv : 0) + (size_t)TM_ROWS * dk + (size_t)TM_ROWS * TM_KEYS) * sizeof(float);
+  EL_REFUSE(smem <= 227 * 1024, "masked_attn_tiled: heads of %d / %d need %zu bytes of shared memory", dk, dv, smem);
+  auto kern = masked_attn_tiled_kernel<T, TO, NC>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int grp = H / G;
+  const dim3 grid(n_tiles, G, (max_tile_tokens * grp + TM_ROWS - 1) / TM_ROWS);
+  launch_pdl(0, kern, grid, dim3(TM_WARPS * 32), smem, stream, q, (TO*)out, (const T*)kcache, (const T*)vcache, page_table, table_stride, n_pages,
+             tile_seq, tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, mask, mask_size, sink);
+  return 0;
+}
+
+extern "C" int edgelm_masked_attn_tiled(const float* q, void* out, int out_dtype, const void* kcache, const void* vcache, int dtype,
+                                        const int32_t* page_table, int table_stride, int n_pages, const int32_t* tile_seq,
+                                        const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles,
+                                        int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
+                                        const float* sink, cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  if (masked_common_check("masked_attn_tiled", H, G, dk, dv, mask, mask_size, dtype, out_dtype)) return -1;
+  EL_REFUSE(n_tiles > 0 && max_tile_tokens > 0 && G <= 65535, "masked_attn_tiled: bad tile counts");
+  EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn_tiled: values of %d inside keys of %d", dv, dk);
+  int rc = 0;
+#define EL_MT2(T, TO, NC) rc = launch_masked_tiled<T, TO, NC>(q, out, kcache, vcache, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, mask, mask_size, sink, stream)
+#define EL_MT(NC) do { if (dtype == DT_F32) EL_MT2(float, float, NC); else if (out_dtype == DT_F32) EL_MT2(__nv_bfloat16, float, NC); else EL_MT2(__nv_bfloat16, __nv_bfloat16, NC); } while (0)
+  if (dv <= 32) EL_MT(1); else if (dv <= 64) EL_MT(2); else if (dv <= 128) EL_MT(4); else if (dv <= 256) EL_MT(8); else EL_MT(16);
+#undef EL_MT
+#undef EL_MT2
+  if (rc != 0) return rc;
+  EL_LAUNCH_CHECK("masked_attn_tiled");
+  return 0;
+}

@@ -7,10 +7,10 @@
 
 namespace edgelm {
 
-// ---------------------------------------------------------------- embedding: x[t,:] = E[id_t,:]
+// ---------------------------------------------------------------- embedding: x[t,:] = E[id_t,:] * scale
 template <typename TW>
 __global__ void embed_gather_kernel(const int32_t* __restrict__ ids, const TW* __restrict__ table,
-                                    float* __restrict__ x, int dim, int vocab, int* __restrict__ err) {
+                                    float* __restrict__ x, int dim, int vocab, float scale, int* __restrict__ err) {
   const int t = blockIdx.x;
   const int id = ids[t];
   if (id < 0 || id >= vocab) {  // the host checks ids that it has seen; ids sampled on the device are checked here
@@ -19,7 +19,7 @@ __global__ void embed_gather_kernel(const int32_t* __restrict__ ids, const TW* _
     return;
   }
   const TW* row = table + (size_t)id * dim;
-  for (int i = threadIdx.x; i < dim; i += blockDim.x) x[(size_t)t * dim + i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) x[(size_t)t * dim + i] = to_f32(row[i]) * scale;
 }
 
 // ---------------------------------------------------------------- RMSNorm
@@ -219,14 +219,14 @@ __global__ void rope_kv_append_vec_kernel(__nv_bfloat16* __restrict__ qkv, const
 using namespace edgelm;
 
 extern "C" int edgelm_embed_gather(const int32_t* ids, const void* table, int table_dtype, float* x, int n_tokens,
-                                   int dim, int vocab, int* err, cudaStream_t stream) {
+                                   int dim, int vocab, float scale, int* err, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && dim > 0 && vocab > 0, "embed_gather: bad sizes tokens=%d dim=%d vocab=%d", n_tokens, dim, vocab);
   const int threads = dim >= 256 ? 256 : 128;
   if (table_dtype == DT_F32)
-    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, x, dim, vocab, err);
+    embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, x, dim, vocab, scale, err);
   else if (table_dtype == DT_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, dim, vocab, err);
+    embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(ids, (const __nv_bfloat16*)table, x, dim, vocab, scale, err);
   else
     EL_REFUSE(false, "embed_gather: unknown dtype code %d", table_dtype);
   EL_LAUNCH_CHECK("embed_gather");

@@ -1,0 +1,237 @@
+// A feed-forward made of experts, of which every token uses the `top` with the largest router logits.
+//
+//   route     logits z = Wr h + br in float32 (a warp a token); the `top` largest (first maximum on ties), and their
+//             weights: the softmax over the chosen logits only.
+//   plan      the (token, choice) pairs are grouped by expert: rows of a padded layout in which every expert's rows
+//             start at a multiple of the row tile, so that a tile of rows belongs to one expert.
+//             row_pair[row] = pair (token * top + choice) or -1; tile_expert[tile] = expert or -1.
+//   products  mid[row] = silu(Wg_e h) * (Wu_e h) for the row's token; y[pair] = Wd_e mid[row] (float32).
+//   combine   x[t] += sum_k weight[t][k] * y[t * top + k], in the order of k.
+// Every row is computed by itself, so a token's result does not depend on what else is in the step.
+#include "common.cuh"
+
+namespace edgelm {
+
+constexpr int MOE_MAX_EXPERTS = 1024;
+
+template <typename TH>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int32_t* __restrict__ idx,
+                 float* __restrict__ wts, int n_tokens, int D, int E, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float mr_logits[];       // [warps][E]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
+  const int t = blockIdx.x * NW + warp;
+  if (t >= n_tokens) return;
+  float* z = mr_logits + warp * E;
+  const TH* row = h + (size_t)t * D;
+  for (int e = 0; e < E; ++e) {
+    const float* w = wr + (size_t)e * D;
+    float a0 = 0.f, a1 = 0.f;
+    int i = lane;
+    for (; i + 32 < D; i += 64) { a0 = fmaf(to_f32(row[i]), w[i], a0); a1 = fmaf(to_f32(row[i + 32]), w[i + 32], a1); }
+    if (i < D) a0 = fmaf(to_f32(row[i]), w[i], a0);
+    const float s = warp_sum(a0 + a1);
+    if (lane == 0) z[e] = s + br[e];
+  }
+  __syncwarp();
+  if (lane == 0) {
+    float zmax = 0.f, sum = 0.f;
+    for (int k = 0; k < top; ++k) {
+      int best = -1;
+      float bz = -INFINITY;
+      for (int e = 0; e < E; ++e)
+        if (z[e] > bz) { bz = z[e]; best = e; }
+      if (best < 0) best = 0;     // (every logit was NaN or -inf)
+      if (k == 0) zmax = bz;
+      const float p = expf(bz - zmax);
+      idx[(size_t)t * top + k] = best;
+      wts[(size_t)t * top + k] = p;
+      sum += p;
+      z[best] = -INFINITY;
+    }
+    const float inv = 1.0f / sum;
+    for (int k = 0; k < top; ++k) wts[(size_t)t * top + k] *= inv;
+  }
+}
+
+// One block.  counts -> padded offsets -> rows.  The order of an expert's rows depends on the order in which the threads
+// arrive; no result does, since every row is computed by itself.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int32_t* __restrict__ idx, int n_pairs, int E, int tile_rows, int max_tiles, int32_t* __restrict__ row_pair,
+                int32_t* __restrict__ tile_expert) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int counts[MOE_MAX_EXPERTS], offs[MOE_MAX_EXPERTS];
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;
+  for (int i = threadIdx.x; i < max_tiles * tile_rows; i += blockDim.x) row_pair[i] = -1;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = idx[i];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int tile = 0;
+    for (int e = 0; e < E; ++e) {
+      offs[e] = tile * tile_rows;
+      const int nt = (counts[e] + tile_rows - 1) / tile_rows;
+      for (int j = 0; j < nt && tile < max_tiles; ++j) tile_expert[tile++] = e;
+      counts[e] = 0;
+    }
+    for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
+    const int e = idx[i];
+    if (e >= 0 && e < E) {
+      const int r = offs[e] + atomicAdd(&counts[e], 1);
+      if (r < max_tiles * tile_rows) row_pair[r] = i;
+    }
+  }
+}
+
+// The products on the CUDA cores (float32 sums): tiles of 32 rows x 64 columns, K in steps of 32 through shared memory.
+//   GATED: a[row] = h[row_pair[row] / top]; out[row][n] = silu(a . wg_e[n]) * (a . wu_e[n])          (mid, type T)
+//   else:  a[row] = mid[row];               y[row_pair[row]][n] = a . w_e[n]                          (float32)
+constexpr int MG_TM = 32, MG_TN = 64, MG_KC = 32;
+
+template <typename T, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, const T* __restrict__ w2, void* __restrict__ out, int ldo,
+                const int32_t* __restrict__ row_pair, const int32_t* __restrict__ tile_expert, int top, int K, int N) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = tile_expert[blockIdx.x];
+  if (e < 0) return;
+  __shared__ float As[MG_TM][MG_KC + 1];
+  __shared__ float Ws[MG_TN][MG_KC + 1];
+  __shared__ float W2s[GATED ? MG_TN : 1][MG_KC + 1];
+  __shared__ int pair_of[MG_TM];
+  const int r0 = blockIdx.x * MG_TM, n0 = blockIdx.y * MG_TN;
+  if (threadIdx.x < MG_TM) pair_of[threadIdx.x] = row_pair[r0 + threadIdx.x];
+  __syncthreads();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const T* we = w + (size_t)e * N * K;
+  const T* w2e = GATED ? w2 + (size_t)e * N * K : nullptr;
+  float acc[2][4] = {}, acc2[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += MG_KC) {
+    for (int i = threadIdx.x; i < MG_TM * MG_KC; i += 256) {
+      const int r = i / MG_KC, k = i - r * MG_KC;
+      const int p = pair_of[r];
+      float v = 0.f;
+      if (p >= 0 && k0 + k < K) v = to_f32(a[(size_t)(GATED ? p / top : r0 + r) * lda + k0 + k]);
+      As[r][k] = v;
+    }
+    for (int i = threadIdx.x; i < MG_TN * MG_KC; i += 256) {
+      const int r = i / MG_KC, k = i - r * MG_KC;
+      const bool in = n0 + r < N && k0 + k < K;
+      Ws[r][k] = in ? to_f32(we[(size_t)(n0 + r) * K + k0 + k]) : 0.f;
+      if (GATED) W2s[r][k] = in ? to_f32(w2e[(size_t)(n0 + r) * K + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < MG_KC; ++k) {
+      const float a0 = As[ty * 2][k], a1 = As[ty * 2 + 1][k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float wv = Ws[tx + 16 * j][k];
+        acc[0][j] = fmaf(a0, wv, acc[0][j]);
+        acc[1][j] = fmaf(a1, wv, acc[1][j]);
+        if (GATED) {
+          const float w2v = W2s[tx + 16 * j][k];
+          acc2[0][j] = fmaf(a0, w2v, acc2[0][j]);
+          acc2[1][j] = fmaf(a1, w2v, acc2[1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = ty * 2 + i, p = pair_of[r];
+    if (p < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx + 16 * j;
+      if (n >= N) continue;
+      if (GATED) {
+        const float z = acc[i][j];
+        ((T*)out)[(size_t)(r0 + r) * ldo + n] = from_f32<T>(z / (1.0f + expf(-z)) * acc2[i][j]);
+      } else {
+        ((float*)out)[(size_t)p * ldo + n] = acc[i][j];
+      }
+    }
+  }
+}
+
+// x[t][:] += sum_k wts[t][k] * y[t * top + k][:]
+__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wts, int top, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k) acc = fmaf(wts[(size_t)t * top + k], y[((size_t)t * top + k) * D + i], acc);
+    x[(size_t)t * D + i] += acc;
+  }
+}
+
+}  // namespace edgelm
+
+using namespace edgelm;
+
+extern "C" int edgelm_moe_tile_rows() { return MG_TM; }
+
+extern "C" int edgelm_moe_route(const void* h, int dtype, const float* wr, const float* br, int32_t* idx, float* wts, int n_tokens, int D,
+                                int E, int top, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && D > 0 && E >= 1 && E <= MOE_MAX_EXPERTS && top >= 1 && top <= E, "moe_route: %d experts, %d chosen", E, top);
+  const int warps = 4;
+  const dim3 grid((n_tokens + warps - 1) / warps), block(warps * 32);
+  const size_t smem = (size_t)warps * E * sizeof(float);
+  const int bit = pdl_bit_for_tokens(n_tokens);
+  if (dtype == DT_F32) launch_pdl(bit, moe_route_kernel<float>, grid, block, smem, stream, (const float*)h, wr, br, idx, wts, n_tokens, D, E, top);
+  else if (dtype == DT_BF16) launch_pdl(bit, moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream, (const __nv_bfloat16*)h, wr, br, idx, wts, n_tokens, D, E, top);
+  else EL_REFUSE(false, "moe_route: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("moe_route");
+  return 0;
+}
+
+extern "C" int edgelm_moe_plan(const int32_t* idx, int n_pairs, int E, int tile_rows, int max_tiles, int32_t* row_pair, int32_t* tile_expert,
+                               cudaStream_t stream) {
+  if (n_pairs == 0) return 0;
+  EL_REFUSE(n_pairs > 0 && E >= 1 && E <= MOE_MAX_EXPERTS && tile_rows >= 1, "moe_plan: bad sizes");
+  EL_REFUSE(max_tiles >= n_pairs / tile_rows + E || max_tiles >= n_pairs, "moe_plan: %d tiles of %d rows cannot hold %d pairs of %d experts", max_tiles, tile_rows, n_pairs, E);
+  launch_pdl(pdl_bit_for_tokens(n_pairs), moe_plan_kernel, dim3(1), dim3(1024), (size_t)0, stream, idx, n_pairs, E, tile_rows, max_tiles, row_pair, tile_expert);
+  EL_LAUNCH_CHECK("moe_plan");
+  return 0;
+}
+
+// gated != 0: the gate and up products with the activation; a = the tokens' rows [tokens][K]; out = mid [rows][N] in `dtype`.
+// gated == 0: the down product; a = mid [rows][K]; out = y [pairs][N] float32.
+extern "C" int edgelm_moe_gemm(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, const int32_t* row_pair,
+                               const int32_t* tile_expert, int max_tiles, int top, int K, int N, int dtype, int gated, cudaStream_t stream) {
+  if (max_tiles == 0) return 0;
+  EL_REFUSE(max_tiles > 0 && K > 0 && N > 0 && top >= 1, "moe_gemm: bad sizes");
+  const dim3 grid(max_tiles, (N + MG_TN - 1) / MG_TN), block(256);
+  const int bit = pdl_bit_for_tokens(max_tiles);
+#define EL_MG(T, GATED) launch_pdl(bit, moe_gemm_kernel<T, GATED>, grid, block, (size_t)0, stream, (const T*)a, lda, (const T*)w, (const T*)w2, out, ldo, row_pair, tile_expert, top, K, N)
+  if (dtype == DT_F32 && gated) EL_MG(float, true);
+  else if (dtype == DT_F32) EL_MG(float, false);
+  else if (dtype == DT_BF16 && gated) EL_MG(__nv_bfloat16, true);
+  else if (dtype == DT_BF16) EL_MG(__nv_bfloat16, false);
+  else EL_REFUSE(false, "moe_gemm: unknown dtype code %d", dtype);
+#undef EL_MG
+  EL_LAUNCH_CHECK("moe_gemm");
+  return 0;
+}
+
+extern "C" int edgelm_moe_combine(float* x, const float* y, const float* wts, int n_tokens, int top, int D, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && top >= 1 && D > 0, "moe_combine: bad sizes");
+  launch_pdl(pdl_bit_for_tokens(n_tokens), moe_combine_kernel, dim3(n_tokens), dim3(D >= 1024 ? 256 : 128), (size_t)0, stream, x, y, wts, top, D);
+  EL_LAUNCH_CHECK("moe_combine");
+  return 0;
+}

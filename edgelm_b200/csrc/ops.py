@@ -96,13 +96,13 @@ def _i32(t, name):
     _need(t.dtype == torch.int32 and t.is_cuda and t.is_contiguous(), f"{name} must be a contiguous int32 CUDA tensor")
 
 
-def embed_gather(ids, table, x, err):
-    """x[t, :] = table[ids[t], :] as float32; ids outside the table set bit 1 of `err`."""
+def embed_gather(ids, table, x, err, scale=1.0):
+    """x[t, :] = table[ids[t], :] * scale as float32; ids outside the table set bit 1 of `err`."""
     _i32(ids, "ids")
     _need(table.dim() == 2 and table.is_contiguous() and x.dtype == torch.float32 and x.is_contiguous(), "embed_gather: layout")
     _need(x.shape == (ids.numel(), table.shape[1]), "embed_gather: x has the wrong shape")
     _check(lib().edgelm_embed_gather(_p(ids), _p(table), _dt(table), _p(x), ids.numel(), table.shape[1], table.shape[0],
-                                     _p(err), _stream()))
+                                     ctypes.c_float(scale), _p(err), _stream()))
 
 
 def rmsnorm(x, w, eps, out, rows_idx=None):
@@ -627,3 +627,184 @@ def pooled_window_attn_tiled(q, out, kcache, vcache, pooled_k, pooled_v, page_ta
                                                  _p(pooled_v) if pool else _p(None), _p(page_table), page_table.stride(0), kcache.shape[0],
                                                  _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles), int(max_tile_tokens),
                                                  nh, nkv, dk, dv, ctypes.c_float(scale), int(window), int(pool or 0), rows, _stream()))
+
+
+# ----------------------------------------------------------------------------- attention with a key range per query
+MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
+
+
+def _masked_cache_check(kcache, vcache, nkv, dk, dv, what):
+    _need(kcache.is_contiguous() and tuple(kcache.shape[1:]) == (nkv, PAGE, dk), f"{what}: key cache shape")
+    if vcache is not None:
+        _need(vcache.is_contiguous() and vcache.dtype == kcache.dtype and tuple(vcache.shape) == (kcache.shape[0], nkv, PAGE, dv), f"{what}: value cache shape")
+    else:
+        _need(dv <= dk, f"{what}: values of {dv} dimensions inside keys of {dk}")
+
+
+def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache, nh, nkv, dk, dv, rot, interleaved, freq, err):
+    """qkv [T, nh dk + nkv dk + nkv dv] float32 (+ bias): the first `rot` dimensions of every query and key head are rotated
+    by position * freq (float64 frequencies; pairs (2i, 2i + 1) if `interleaved`, else (i, i + rot/2)); queries go to q_out
+    [T, nh dk] float32, keys and values to their places in the cache pages."""
+    _f32(qkv, "qkv"); _f32(q_out, "q_out")
+    T = qkv.shape[0]
+    _need(qkv.shape[1] == (nh + nkv) * dk + nkv * dv and q_out.shape == (T, nh * dk), "rotate_append: shapes")
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == qkv.shape[1]), "rotate_append: bias")
+    _need(rot == 0 or (freq is not None and freq.dtype == torch.float64 and freq.numel() == rot // 2 and freq.is_contiguous()), "rotate_append: frequencies")
+    _masked_cache_check(kcache, vcache, nkv, dk, dv, "rotate_append")
+    _need(vcache is not None, "rotate_append: values need a cache of their own")
+    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (page_table, "page_table")):
+        _i32(t, n)
+    _check(lib().edgelm_rotate_append(_p(qkv), _p(bias), _p(q_out), _p(tok_pos), _p(tok_seq), _p(page_table), page_table.stride(0),
+                                      kcache.shape[0], _p(kcache), _p(vcache), _dt(kcache), T, nh, nkv, dk, dv, int(rot),
+                                      1 if interleaved else 0, _p(freq), _p(err), _stream()))
+
+
+def latent_prepare(u, kv_off, has_kv, q_full, norm_w, eps, tok_pos, tok_seq, page_table, kcache, nh, d, rd, r, freq, err):
+    """u [T, *] float32: nh query heads of [d | rd] from column 0 and, with `has_kv`, the latent's row [r | rd] from column
+    `kv_off`.  The rotated part of every query head (pairs (i, i + rd/2)) goes to q_full[t, h, r:]; the latent, RMS-normed
+    with `norm_w`, and the rotated shared key part become the token's cache row [r + rd]."""
+    _f32(u, "u"); _f32(q_full, "q_full")
+    T = u.shape[0]
+    _need(q_full.shape == (T, nh * (r + rd)), "latent_prepare: q_full shape")
+    _need(rd == 0 or (freq is not None and freq.dtype == torch.float64 and freq.numel() == rd // 2 and freq.is_contiguous()), "latent_prepare: frequencies")
+    if has_kv:
+        _f32(norm_w, "norm_w")
+        _need(norm_w.numel() == r, "latent_prepare: the norm's weight")
+        _masked_cache_check(kcache, None, 1, r + rd, r, "latent_prepare")
+        _i32(page_table, "page_table")
+    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq")):
+        _i32(t, n)
+    _check(lib().edgelm_latent_prepare(_p(u), u.stride(0), int(kv_off), 1 if has_kv else 0, _p(q_full), _p(norm_w) if has_kv else _p(None),
+                                       ctypes.c_float(eps), _p(tok_pos), _p(tok_seq), _p(page_table) if has_kv else _p(None),
+                                       page_table.stride(0) if has_kv else 0, kcache.shape[0] if has_kv else 0,
+                                       _p(kcache) if has_kv else _p(None), _dt(kcache) if has_kv else F32, T, nh, d, rd, r, _p(freq), _p(err), _stream()))
+
+
+def head_matmul(a, a_head_stride, w, out, out_head_stride):
+    """out[t, h * out_head_stride + n] = sum_k a[t, h * a_head_stride + k] * w[h, n, k]: one small product per head.
+    a float32 rows; w [heads, N, K] float32 or bfloat16; out float32 or the weights' type."""
+    _f32(a, "a")
+    _need(w.dim() == 3 and w.is_contiguous() and out.stride(1) == 1 and a.stride(1) == 1, "head_matmul: layout")
+    H, N, K = w.shape
+    _need((H - 1) * a_head_stride + K <= a.shape[1] and (H - 1) * out_head_stride + N <= out.shape[1] and out.shape[0] == a.shape[0], "head_matmul: shapes")
+    _check(lib().edgelm_head_matmul(_p(a), a.stride(0), int(a_head_stride), _p(w), _dt(w), _p(out), _dt(out), out.stride(0), int(out_head_stride),
+                                    a.shape[0], H, K, N, _stream()))
+
+
+def add_row_bias(x, b):
+    """x[t, :] += b."""
+    _f32(x, "x"); _f32(b, "b")
+    _need(x.dim() == 2 and b.numel() == x.shape[1], "add_row_bias: shapes")
+    _check(lib().edgelm_add_row_bias(_p(x), _p(b), x.shape[0], x.shape[1], _stream()))
+
+
+def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, dk, dv, scale, mask, mask_size, sink, max_keys):
+    """Attention of every token of the step over the keys lo .. its position (`mask`: MASK_CAUSAL lo = 0; MASK_WINDOW the
+    last `mask_size` keys; MASK_CHUNK the keys of its own chunk of `mask_size` positions).  q [T, nh dk] float32; out
+    [T, nh dv] float32 or the cache's type; `vcache` None: a value is the first dv dimensions of its key row.  `sink`
+    (float32 [nh] or None): one more term exp(sink_h) in the denominator.  `max_keys`: the most keys a token sees."""
+    _f32(q, "q")
+    T = q.shape[0]
+    _need(q.shape == (T, nh * dk) and out.is_contiguous() and out.shape == (T, nh * dv), "masked_attn: shapes")
+    _masked_cache_check(kcache, vcache, nkv, dk, dv, "masked_attn")
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh), "masked_attn: sink")
+    for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (page_table, "page_table")):
+        _i32(t, n)
+    _check(lib().edgelm_masked_attn(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(tok_pos), _p(tok_seq), _p(page_table),
+                                    page_table.stride(0), kcache.shape[0], T, nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0),
+                                    _p(sink), int(max_keys), _stream()))
+
+
+def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv,
+                      dk, dv, scale, mask, mask_size, sink):
+    """`masked_attn` for prompt steps: the step's tokens come as tiles (runs of at most `max_tile_tokens` consecutive tokens of
+    one sequence); a page of keys and values is staged once for all the rows of a tile."""
+    _f32(q, "q")
+    T = q.shape[0]
+    _need(q.shape == (T, nh * dk) and out.is_contiguous() and out.shape == (T, nh * dv), "masked_attn_tiled: shapes")
+    _masked_cache_check(kcache, vcache, nkv, dk, dv, "masked_attn_tiled")
+    _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh), "masked_attn_tiled: sink")
+    for t, n in ((page_table, "page_table"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
+        _i32(t, n)
+    _check(lib().edgelm_masked_attn_tiled(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(page_table), page_table.stride(0),
+                                          kcache.shape[0], _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles),
+                                          int(max_tile_tokens), nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0), _p(sink), _stream()))
+
+
+# ----------------------------------------------------------------------------- gated delta rule
+def delta_prepare(qkv, u, b_off, a_off, a_log, dt_bias, bg, heads, kv_heads, d, e, unit_eps, q_scale):
+    """qkv [T, G d | G d | H e] float32, in place: every query and key head becomes x / sqrt(sum(x^2) + unit_eps), queries
+    also times q_scale.  bg [T, 2 H] receives beta = sigmoid(u[:, b_off + h]) and the decay exp(-exp(A_log_h)
+    softplus(u[:, a_off + h] + dt_bias_h))."""
+    for t, n in ((qkv, "qkv"), (a_log, "A_log"), (dt_bias, "dt_bias"), (bg, "bg")):
+        _f32(t, n)
+    _need(u.dtype == torch.float32 and u.stride(1) == 1 and u.shape[0] == qkv.shape[0] and bg.numel() >= 2 * heads * qkv.shape[0], "delta_prepare: shapes")
+    _need(a_log.numel() == heads and dt_bias.numel() == heads, "delta_prepare: per-head vectors")
+    _check(lib().edgelm_delta_prepare(_p(qkv), qkv.shape[1], _p(u), u.stride(0), int(b_off), int(a_off), _p(a_log), _p(dt_bias), _p(bg),
+                                      qkv.shape[0], heads, kv_heads, d, e, ctypes.c_float(unit_eps), ctypes.c_float(q_scale), _stream()))
+
+
+def delta_scan(qkv, bg, state, o, seq_tok0, seq_slot, n_seqs, heads, kv_heads, d, e):
+    """Per head: S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, over the step's tokens of every sequence.
+    qkv [T, G d | G d | H e] (prepared), bg [T, 2 H] (beta, decay), state [slots, H, e, d] float32, o [T, H e]."""
+    for t, n in ((qkv, "qkv"), (bg, "bg"), (state, "state"), (o, "o")):
+        _f32(t, n)
+    T = qkv.shape[0]
+    _need(tuple(state.shape[1:]) == (heads, e, d) and o.shape == (T, heads * e), "delta_scan: state or output shape")
+    _check(lib().edgelm_delta_scan(_p(qkv), qkv.shape[1], _p(bg), _p(state), _p(o), _p(seq_tok0), _p(seq_slot), int(n_seqs), T, heads,
+                                   kv_heads, d, e, _stream()))
+
+
+# ----------------------------------------------------------------------------- mixture of experts
+def moe_tile_rows():
+    """Rows of a tile of the grouped products: every expert's rows start at a multiple of it."""
+    return int(lib().edgelm_moe_tile_rows())
+
+
+def moe_max_tiles(n_pairs, n_experts, tile_rows):
+    """Row tiles that `n_pairs` (token, choice) pairs grouped by expert take at most."""
+    return max(1, min(n_pairs, n_pairs // tile_rows + n_experts))
+
+
+def moe_route(h, wr, br, idx, wts, top):
+    """Router logits h @ wr.T + br in float32; idx [T, top] the experts with the largest logits (first maximum on ties),
+    wts [T, top] the softmax over the chosen logits."""
+    _f32(wr, "router weight"); _f32(br, "router bias"); _f32(wts, "wts"); _i32(idx, "idx")
+    T, D = h.shape
+    E = wr.shape[0]
+    _need(h.is_contiguous() and wr.shape == (E, D) and br.numel() == E and idx.shape == (T, top) and wts.shape == (T, top), "moe_route: shapes")
+    _check(lib().edgelm_moe_route(_p(h), _dt(h), _p(wr), _p(br), _p(idx), _p(wts), T, D, E, int(top), _stream()))
+
+
+def moe_plan(idx, n_experts, tile_rows, row_pair, tile_expert):
+    """Group the pairs of idx [T, top] by expert: row_pair [max_tiles * tile_rows] (pair or -1), tile_expert [max_tiles]."""
+    _i32(idx, "idx"); _i32(row_pair, "row_pair"); _i32(tile_expert, "tile_expert")
+    max_tiles = tile_expert.numel()
+    _need(row_pair.numel() == max_tiles * tile_rows, "moe_plan: row_pair size")
+    _check(lib().edgelm_moe_plan(_p(idx), idx.numel(), int(n_experts), int(tile_rows), max_tiles, _p(row_pair), _p(tile_expert), _stream()))
+
+
+def moe_gate_up(h, w_gate, w_up, mid, row_pair, tile_expert, top):
+    """mid[row] = silu(w_gate[e] h[t]) * (w_up[e] h[t]) for every row of the plan (t = row_pair[row] // top, e the row's tile's expert)."""
+    E, N, K = w_gate.shape
+    _need(h.dtype == w_gate.dtype == w_up.dtype == mid.dtype and h.is_contiguous() and w_gate.is_contiguous() and w_up.is_contiguous() and mid.is_contiguous(), "moe_gate_up: layout")
+    _need(h.shape[1] == K and w_up.shape == w_gate.shape and mid.shape == (row_pair.numel(), N), "moe_gate_up: shapes")
+    _check(lib().edgelm_moe_gemm(_p(h), h.stride(0), _p(w_gate), _p(w_up), _p(mid), mid.stride(0), _p(row_pair), _p(tile_expert),
+                                 tile_expert.numel(), int(top), K, N, _dt(h), 1, _stream()))
+
+
+def moe_down(mid, w_down, y, row_pair, tile_expert, top):
+    """y[pair] = w_down[e] mid[row] (float32) for every row of the plan."""
+    E, N, K = w_down.shape
+    _f32(y, "y")
+    _need(mid.dtype == w_down.dtype and mid.is_contiguous() and w_down.is_contiguous() and mid.shape == (row_pair.numel(), K) and y.shape[1] == N, "moe_down: shapes")
+    _check(lib().edgelm_moe_gemm(_p(mid), mid.stride(0), _p(w_down), _p(None), _p(y), y.stride(0), _p(row_pair), _p(tile_expert),
+                                 tile_expert.numel(), int(top), K, N, _dt(mid), 0, _stream()))
+
+
+def moe_combine(x, y, wts):
+    """x[t] += sum_k wts[t, k] * y[t * top + k]."""
+    _f32(x, "x"); _f32(y, "y"); _f32(wts, "wts")
+    T, top = wts.shape
+    _need(x.shape[0] == T and y.shape == (T * top, x.shape[1]), "moe_combine: shapes")
+    _check(lib().edgelm_moe_combine(_p(x), _p(y), _p(wts), T, top, x.shape[1], _stream()))

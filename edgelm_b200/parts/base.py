@@ -43,12 +43,15 @@ class KVNeed:
     """Keys and values for every position (`window` None) or for the last `window` positions.  `v_head_dim`: the
     size of a value head where it differs from a key head's.  `pool`: beside the pages, one float32 key and value
     row per block of `pool` consecutive positions (the block's mean, written by the mixer when the block is full),
-    kept in the page that holds the block's last position: `CacheEntry.pooled_k / pooled_v`."""
+    kept in the page that holds the block's last position: `CacheEntry.pooled_k / pooled_v`.  `values_in_keys`: no
+    value rows of their own are kept (a latent that is key and value at once: the mixer reads its values out of the
+    key rows); `CacheEntry.v` is then None."""
     n_kv_heads: int
     head_dim: int
     window: int = None
     v_head_dim: int = None
     pool: int = None
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

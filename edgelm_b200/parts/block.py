@@ -1,5 +1,5 @@
 """Arrangements of one layer's parts.  "prenorm": x += mixer(norm1(x)); x += ffn(norm2(x))
-(adarsh-sgh/edgelm tools/elm.py:122-153).  "sublayer_norm": x += norm1(mixer(x)); x += norm2(ffn(x)), with an
+(adarsh-sgh/edgelm tools/elm.py:122-153); a layer may have no feed-forward.  "sublayer_norm": x += norm1(mixer(x)); x += norm2(ffn(x)), with an
 optional blend of the mixer's input with the previous token's."""
 import torch
 
@@ -17,9 +17,9 @@ class PreNormBlock(Part):
         self.dtype = env.dtype
         self.mixer_norm = env.build("norm", layer_spec.mixer_norm)
         self.mixer = env.build("mixer", layer_spec.mixer)
-        self.ffn_norm = env.build("norm", layer_spec.ffn_norm)
-        self.ffn = env.build("ffn", layer_spec.ffn)
-        self.parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+        self.ffn_norm = env.build("norm", layer_spec.ffn_norm) if layer_spec.ffn is not None else None
+        self.ffn = env.build("ffn", layer_spec.ffn) if layer_spec.ffn is not None else None
+        self.parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None)
         self.hidden = layer_spec.mixer_norm["dim"]
 
     def weight_shapes(self, prefix=None):
@@ -38,14 +38,16 @@ class PreNormBlock(Part):
     def sizes(self):
         out = {}
         for p in (self.mixer, self.ffn, self.mixer_norm):
-            out.update(p.sizes())
+            if p is not None:
+                out.update(p.sizes())
         return out
 
     def flops(self, n_tokens, attended):
         return sum(p.flops(n_tokens, attended) for p in self.parts)
 
     def describe(self):
-        return f"{self.kind}: {self.mixer_norm.describe()} -> {self.mixer.describe()}; {self.ffn_norm.describe()} -> {self.ffn.describe()}"
+        ffn = f"; {self.ffn_norm.describe()} -> {self.ffn.describe()}" if self.ffn is not None else ""
+        return f"{self.kind}: {self.mixer_norm.describe()} -> {self.mixer.describe()}{ffn}"
 
     def tile_sizes(self):
         return tuple(self.mixer.tile_sizes())
@@ -56,7 +58,7 @@ class PreNormBlock(Part):
 
     def workspace_bytes(self, n_tokens, n_seqs):
         return nbytes((n_tokens, self.hidden), self.dtype) + max(self.mixer.workspace_bytes(n_tokens, n_seqs),
-                                                                  self.ffn.workspace_bytes(n_tokens, n_seqs))
+                                                                  self.ffn.workspace_bytes(n_tokens, n_seqs) if self.ffn is not None else 0)
 
     def _normed(self, ctx, x, norm, part):
         """The part's input: lazily normalised if both the norm and the part can work that way
@@ -76,12 +78,14 @@ class PreNormBlock(Part):
         # it on its way into L2): after the mixer the feed-forward's first weights, after that whatever the caller
         # named as coming after this layer
         after_layer = ctx.weights_after
-        ctx.weights_after = self.ffn.first_weights()
+        if self.ffn is not None:
+            ctx.weights_after = self.ffn.first_weights()
         with ctx.ws.frame():
             self.mixer.forward(ctx, self._normed(ctx, x, self.mixer_norm, self.mixer), x, cache)
         ctx.weights_after = after_layer
-        with ctx.ws.frame():
-            self.ffn.forward(ctx, self._normed(ctx, x, self.ffn_norm, self.ffn), x)
+        if self.ffn is not None:
+            with ctx.ws.frame():
+                self.ffn.forward(ctx, self._normed(ctx, x, self.ffn_norm, self.ffn), x)
 
 
 @register_block("sublayer_norm")

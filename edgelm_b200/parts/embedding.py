@@ -1,4 +1,4 @@
-"""Token embedding: x[t] = E[id_t] (adarsh-sgh/edgelm src/kernels_ref.cpp:41-46), no scaling."""
+"""Token embedding: x[t] = E[id_t] (adarsh-sgh/edgelm src/kernels_ref.cpp:41-46), times `scale` (1 unless the spec names one)."""
 from ..csrc import ops
 from .base import Part, as_matrix
 from .registry import register_embedding
@@ -9,11 +9,15 @@ class Embedding(Part):
     graph_safe = True
     def __init__(self, spec, env):
         self.vocab_size, self.dim, self.name = spec["vocab_size"], spec["dim"], spec["name"]
+        self.scale = float(spec.get("scale") or 1.0)
         self.dtype = env.dtype
         self.table = None
 
     def sizes(self):
-        return {"vocab": self.vocab_size, "hidden": self.dim}
+        out = {"vocab": self.vocab_size, "hidden": self.dim}
+        if self.scale != 1.0:
+            out["embedding_scale"] = self.scale
+        return out
 
     def weight_shapes(self, prefix=""):
         return {self.name: (self.vocab_size, self.dim)}
@@ -22,4 +26,4 @@ class Embedding(Part):
         self.table = as_matrix(tensors[self.name], self.dtype, device)
 
     def forward(self, ctx, x):
-        ops.embed_gather(ctx.token_ids, self.table, x, ctx.err)
+        ops.embed_gather(ctx.token_ids, self.table, x, ctx.err, self.scale)

@@ -1,0 +1,147 @@
+"""Grouped-query attention whose queries see a range of keys, with an optional sink in the softmax.
+
+q, k, v are projections of the mixer's input (one matrix product over the three weights stacked; its float32 sums are
+kept), with optional biases on q, k, v and the output projection.  The first `rot_dims` dimensions of every query and key
+head are rotated by position * f_i, with neighbouring pairs (2i, 2i + 1) (`rot_pairs` "interleaved") or half-split
+pairs (i, i + rot_dims / 2) ("half"); the frequencies are base^(-2i / rot_dims), optionally with the long wavelengths
+stretched (`parts.rope.rotary_frequencies`).  score = (q . k) * scale.  The mask (`mask`: {"kind", "size"}):
+
+    causal   position i sees every j <= i
+    window   the last `size` keys, its own included
+    chunk    the j <= i of its own chunk, floor(i / size) = floor(j / size), counted from the sequence's first position
+
+With `sink` (a tensor's name) the softmax's denominator has one more term exp(sink_h) per query head, which has no key
+and no value and is not scaled.  A value head may have another size than a key head.  Angles, scores, the softmax and
+the weighted values are float32 in both precisions; keys and values are kept in the compute dtype.
+"""
+import torch
+
+from ..config.base import ConfigError
+from ..csrc import ops
+from . import linear
+from .base import KVNeed, Part, as_matrix, as_vector, nbytes
+from .registry import register_mixer
+from .rope import rotary_frequencies
+
+MASKS = {"causal": ops.MASK_CAUSAL, "window": ops.MASK_WINDOW, "chunk": ops.MASK_CHUNK}
+
+
+def read_mask(mask, where):
+    """(kernel code, size) of a mask spec {"kind", "size"} (None: causal)."""
+    if not mask:
+        return ops.MASK_CAUSAL, 0
+    kind = mask.get("kind", "causal")
+    if kind not in MASKS:
+        raise ConfigError(f"{where}: a mask of kind '{kind}' is not known ({', '.join(MASKS)})")
+    size = int(mask.get("size") or 0)
+    if kind != "causal" and size < 1:
+        raise ConfigError(f"{where}: a {kind} of {size} positions")
+    return MASKS[kind], size
+
+
+def most_keys(mask, size):
+    """The most keys that a token can see under the mask (a bound that does not depend on the step: the choice it
+    drives is frozen into a captured graph)."""
+    return size if mask != ops.MASK_CAUSAL else 1 << 30
+
+
+@register_mixer("masked_attention")
+class MaskedAttention(Part):
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        self.hidden = spec["hidden_size"]
+        self.nh, self.nkv, self.dk = spec["num_heads"], spec["num_kv_heads"], spec["head_dim"]
+        self.dv = spec.get("v_head_dim") or self.dk
+        self.scale = float(spec["scale"])
+        self.rot = int(spec.get("rot_dims") or 0)
+        self.interleaved = spec.get("rot_pairs", "half") == "interleaved"
+        self.rot_base, self.rot_scaling = float(spec.get("rot_base") or 10000.0), spec.get("rot_scaling")
+        self.bias = bool(spec.get("bias", False))
+        self.names = dict(spec["names"])
+        self.dtype = env.dtype
+        if self.nh <= 0 or self.nkv <= 0 or self.nh % self.nkv:
+            raise ConfigError(f"masked_attention: {self.nh} query heads are not a multiple of {self.nkv} key/value heads")
+        if not (1 <= self.dk <= 1024 and 1 <= self.dv <= 512):
+            raise ConfigError(f"masked_attention: head sizes {self.dk} / {self.dv} are not taken (keys to 1024, values to 512)")
+        if self.rot % 2 or not 0 <= self.rot <= self.dk:
+            raise ConfigError(f"masked_attention: {self.rot} rotated dimensions of a head of {self.dk}")
+        self.mask, self.mask_size = read_mask(spec.get("mask"), "masked_attention")
+        self.d_qkv = (self.nh + self.nkv) * self.dk + self.nkv * self.dv
+        self.tile_tokens = max(1, 32 // (self.nh // self.nkv))
+        self.freq = self.b_qkv = self.b_o = self.sink = None
+
+    def tile_sizes(self):
+        return (self.tile_tokens,)
+
+    def sizes(self):
+        out = {"heads": self.nh, "kv_heads": self.nkv, "head_dim": self.dk, "v_head_dim": self.dv, "rot_dims": self.rot,
+               "mask": {v: k for k, v in MASKS.items()}[self.mask], "mask_size": self.mask_size, "sink": "sink" in self.names}
+        return out
+
+    def flops(self, n_tokens, attended):
+        proj = 2.0 * n_tokens * self.hidden * (self.d_qkv + self.nh * self.dv)
+        if self.mask != ops.MASK_CAUSAL:
+            attended = min(attended, n_tokens * self.mask_size)
+        return proj + 2.0 * attended * self.nh * (self.dk + self.dv)
+
+    def weight_shapes(self, prefix):
+        n = self.names
+        out = {prefix + n["q"]: (self.nh * self.dk, self.hidden), prefix + n["k"]: (self.nkv * self.dk, self.hidden),
+               prefix + n["v"]: (self.nkv * self.dv, self.hidden), prefix + n["o"]: (self.hidden, self.nh * self.dv)}
+        if self.bias:
+            out.update({prefix + n["q"] + n["bias"]: (self.nh * self.dk,), prefix + n["k"] + n["bias"]: (self.nkv * self.dk,),
+                        prefix + n["v"] + n["bias"]: (self.nkv * self.dv,), prefix + n["o"] + n["bias"]: (self.hidden,)})
+        if "sink" in n:
+            out[prefix + n["sink"]] = (self.nh,)
+        return out
+
+    def load(self, tensors, prefix, device):
+        n = self.names
+        self.w_qkv = torch.cat([as_matrix(tensors[prefix + n[k]], self.dtype, device) for k in ("q", "k", "v")], dim=0).contiguous()
+        self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
+        if self.bias:
+            self.b_qkv = torch.cat([as_vector(tensors[prefix + n[k] + n["bias"]], device) for k in ("q", "k", "v")]).contiguous()
+            self.b_o = as_vector(tensors[prefix + n["o"] + n["bias"]], device)
+        if "sink" in n:
+            self.sink = as_vector(tensors[prefix + n["sink"]], device)
+        if self.rot:
+            self.freq = rotary_frequencies(self.rot, self.rot_base, self.rot_scaling).to(device).contiguous()
+
+    def first_weights(self):
+        return (self.w_qkv,)
+
+    def cache_need(self):
+        # (a window's pages could be given back as the sequence moves on, `KVNeed.window`; the kernels here read through
+        # the whole table, so every page is kept)
+        return KVNeed(self.nkv, self.dk, None, v_head_dim=self.dv)
+
+    def workspace_bytes(self, n_tokens, n_seqs):
+        return (nbytes((n_tokens, self.d_qkv), torch.float32) + nbytes((n_tokens, self.nh * self.dk), torch.float32) +
+                nbytes((n_tokens, self.nh * self.dv), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype))
+
+    def forward(self, ctx, h, x, cache, accumulate=True):
+        h = linear.as_tensor(h)
+        T, ws = h.shape[0], ctx.ws
+        qkv = ws.alloc((T, self.d_qkv), torch.float32)
+        with ctx.prof("qkv_proj"):
+            linear.matmul(ctx, h, self.w_qkv, qkv, prefetch=(self.w_o,))
+        q = ws.alloc((T, self.nh * self.dk), torch.float32)
+        table = ctx.page_table(cache.group)
+        with ctx.prof("rotate_append"):
+            ops.rotate_append(qkv, self.b_qkv, q, ctx.tok_pos, ctx.tok_seq, table, cache.k, cache.v, self.nh, self.nkv, self.dk, self.dv,
+                              self.rot, self.interleaved, self.freq, ctx.err)
+        a = ws.alloc((T, self.nh * self.dv), self.dtype)
+        with ctx.prof("attn_masked"):
+            if ctx.all_single:
+                ops.masked_attn(q, a, cache.k, cache.v, ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk, self.dv, self.scale,
+                                self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size))
+            else:
+                tiles = ctx.tiles(self.tile_tokens)
+                ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0, tiles.count,
+                                      self.tile_tokens, self.nh, self.nkv, self.dk, self.dv, self.scale, self.mask, self.mask_size, self.sink)
+        with ctx.prof("o_proj"):
+            linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
+                          residual=x if accumulate else None, prefetch=ctx.weights_after)
+            if self.b_o is not None:
+                ops.add_row_bias(x, self.b_o)

@@ -6,6 +6,8 @@ theta^(-2i/head_dim) and angles position * frequency in float64, then rounded to
 kernel that also appends the rotated keys and the raw values to the cache
 (src/kernels_ref.cpp:82-98, 112-118).
 """
+import math
+
 import torch
 
 from ..csrc import ops
@@ -58,3 +60,21 @@ class RotaryPositions(Part):
         position; write the rotated keys and the values into the cache entry's pages."""
         ops.rope_kv_append(qkv, ctx.tok_pos, ctx.tok_seq, ctx.seq_index, ctx.page_table(cache.group), self.cos, self.sin,
                            cache.k, cache.v, n_heads, n_kv_heads, self.head_dim, ctx.err)
+
+
+def rotary_frequencies(dims, base, scaling=None):
+    """Float64 frequencies f_i = base^(-2i / dims), i < dims / 2, for kernels that form position * f_i themselves.
+    `scaling` (optional): a number (every frequency divided by it) or a mapping {factor, low, high, original} that
+    stretches the long wavelengths only: with l = 2 pi / f, f stays where l < original / high, becomes f / factor where
+    l > original / low, and between the two is the blend (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    i = torch.arange(int(dims) // 2, dtype=torch.float64)
+    f = torch.pow(torch.tensor(float(base), dtype=torch.float64), -2.0 * i / int(dims))
+    if scaling is None:
+        return f
+    if not hasattr(scaling, "get"):
+        return f / float(scaling)
+    factor, low, high, original = (float(scaling[k]) for k in ("factor", "low", "high", "original"))
+    wavelength = 2.0 * math.pi / f
+    s = (original / wavelength - low) / (high - low) if high != low else torch.ones_like(f)
+    blend = (1.0 - s) * f / factor + s * f
+    return torch.where(wavelength < original / high, f, torch.where(wavelength > original / low, f / factor, blend))
