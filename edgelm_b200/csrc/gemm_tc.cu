@@ -41,6 +41,14 @@ struct RopeAppend {
   int table_stride, n_pages, max_pos, nh, nkv, hd;
 };
 
+// Grouped products (a feed-forward of experts): the rows of `a` come grouped, every group's rows starting at a multiple of
+// the row tile, and row tile t multiplies the weights of group tile_group[t]: rows group * rows_per_group .. of the
+// stacked weight matrix.  A tile whose group is negative has no rows and is left out.
+struct GroupedTiles {
+  const int32_t* tile_group = nullptr;
+  int rows_per_group = 0;
+};
+
 constexpr int TC_BM = 128;   // rows of `a` per tile = lanes of tensor memory
 constexpr int TC_STAGES = 3;   // ring stages of the one-tile kernel when several blocks share an SM (48 KB stages: 144 KB)
 constexpr int TC_DEEP_BYTES = 192 * 1024;   // ring of the one-tile kernel when the grid is at most one block an SM
@@ -234,7 +242,15 @@ template <int BN, int EPI, typename TOut, int STAGES>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_b2, TOut* out, int ldo, const float* residual,
-               int M, int N, int K, int vec_ok, int* err, int k_splits, float* partial, const RopeAppend rope) {
+               int M, int N, int K, int vec_ok, int* err, int k_splits, float* partial, const RopeAppend rope,
+               const GroupedTiles grp) {
+  // a grouped product is launched without programmatic dependence: the kernel that wrote `tile_group` is complete
+  int w_row0 = blockIdx.x * BN;           // the first row of the weight tile (its output columns start at n0)
+  if (grp.tile_group != nullptr) {
+    const int group = grp.tile_group[blockIdx.y];
+    if (group < 0) return;                // (the whole block, before it holds anything)
+    w_row0 += group * grp.rows_per_group;
+  }
   // k_splits > 1: block z of the grid accumulates its share of K only and leaves the raw sums in
   // `partial` [split][weight][M][N] (float32); splitk_reduce_kernel adds the splits in their order and
   // applies the epilogue.  For products of few tiles and long K (decoding 17 to 128 sequences), which
@@ -286,8 +302,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t sa = smem_u32(smem + i * STAGE_BYTES);
       const int x = (k_first + i) * TC_BK;
       mbar_expect_tx(bar, STAGE_BYTES);
-      tma_load_2d(sa + A_BYTES, &map_b, bar, x, n0);
-      if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, n0);
+      tma_load_2d(sa + A_BYTES, &map_b, bar, x, w_row0);
+      if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, w_row0);
     }
   }
   __syncwarp();
@@ -314,8 +330,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         } else {
           mbar_expect_tx(bar, STAGE_BYTES);
           tma_load_2d(sa, &map_a, bar, x, m0);
-          tma_load_2d(sa + A_BYTES, &map_b, bar, x, n0);
-          if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, n0);
+          tma_load_2d(sa + A_BYTES, &map_b, bar, x, w_row0);
+          if (NB == 2) tma_load_2d(sa + A_BYTES + B_BYTES, &map_b2, bar, x, w_row0);
         }
       }
       __syncwarp();
@@ -606,7 +622,7 @@ static int splitk_for(int tiles, int n_k, size_t bytes_per_split) {
 template <int BN, int EPI, typename TOut>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mb2, void* out, int ldo,
                      const float* residual, int M, int N, int K, int vec_ok, int* err, cudaStream_t stream, bool persistent,
-                     const RopeAppend& rope) {
+                     const RopeAppend& rope, const GroupedTiles& grp = GroupedTiles{}) {
   constexpr int NB = EPI == TC_EPI_SWIGLU ? 2 : 1;
   if (persistent) {
     constexpr int smem = TCP_STAGES * (TC_BM * TC_BK * 2 + NB * BN * TC_BK * 2) + 1024 + 256;
@@ -641,7 +657,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
   constexpr int DEEP = TC_DEEP_BYTES / STAGE_BYTES;   // 6 stages of 32 KB, 8 of 24 KB
   dim3 grid((N + BN - 1) / BN, (M + TC_BM - 1) / TC_BM);
   // (the rotation epilogue is not one the reduce kernel of split products knows: such a product stays whole)
-  const int splits = EPI == TC_EPI_ROPE ? 1 : splitk_for((int)(grid.x * grid.y), (K + TC_BK - 1) / TC_BK, (size_t)NB * M * N * sizeof(float));
+  const int splits = (EPI == TC_EPI_ROPE || grp.tile_group != nullptr) ? 1 : splitk_for((int)(grid.x * grid.y), (K + TC_BK - 1) / TC_BK, (size_t)NB * M * N * sizeof(float));
   grid.z = splits;
   g_last_launches = splits > 1 ? 2 : 1;
   // a grid of at most one block an SM has the shared memory to itself: a deeper ring hides more of the loads' latency
@@ -660,8 +676,8 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, const CUtenso
       set_error("gemm_tc: %d bytes of shared memory refused: %s", smem, cudaGetErrorString(e));
       return -2;
     }
-    cudaError_t le = launch_pdl(8, kern, grid, dim3(TC_THREADS), (size_t)smem, stream, ma, mb, mb2, (TOut*)out, ldo, residual, M, N, K,
-                                vec_ok, err, splits, g_splitk_ws, rope);
+    cudaError_t le = launch_pdl(grp.tile_group != nullptr ? 0 : 8, kern, grid, dim3(TC_THREADS), (size_t)smem, stream, ma, mb, mb2, (TOut*)out, ldo,
+                                residual, M, N, K, vec_ok, err, splits, g_splitk_ws, rope, grp);
     if (le != cudaSuccess) {
       set_error("gemm_tc: launch failed: %s", cudaGetErrorString(le));
       return -2;
@@ -816,6 +832,39 @@ extern "C" int edgelm_gemm_tc(const void* a, int lda, const void* w, const void*
                               cudaStream_t stream) {
   EL_REFUSE(epilogue >= TC_EPI_STORE && epilogue <= TC_EPI_SWIGLU, "gemm_tc: unknown epilogue %d", epilogue);
   return gemm_tc_run(a, lda, w, w2, out, ldo, residual, M, N, K, out_dtype, epilogue, err, stream, RopeAppend{});
+}
+
+// A grouped product: a [M, K] with M a multiple of 128 (rows grouped, every group's first row at a multiple of 128),
+// w [n_groups * N, K] the groups' weights stacked; row tile t uses group tile_group[t] (negative: no rows).  out [M, N].
+// Epilogues: store (float32 or bfloat16) and SwiGLU (w2 the second stacked weight, bfloat16 out).
+extern "C" int edgelm_gemm_tc_grouped(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, int M, int N, int K,
+                                      int n_groups, const int32_t* tile_group, int out_dtype, int epilogue, int* err, cudaStream_t stream) {
+  if (M == 0) return 0;
+  EL_REFUSE(M > 0 && M % TC_BM == 0 && N > 0 && K > 0 && n_groups > 0 && lda >= K && ldo >= N && tile_group != nullptr, "gemm_tc_grouped: bad sizes M=%d N=%d K=%d groups=%d", M, N, K, n_groups);
+  EL_REFUSE(edgelm_gemm_tc_takes(a, lda, w, w2, K), "gemm_tc_grouped: K=%d and lda=%d must be multiples of 8 and the operands 16-byte aligned", K, lda);
+  EL_REFUSE((epilogue == TC_EPI_SWIGLU && w2 != nullptr && out_dtype == DT_BF16) || epilogue == TC_EPI_STORE, "gemm_tc_grouped: epilogue %d with output dtype %d", epilogue, out_dtype);
+  EL_REFUSE(err != nullptr && M / TC_BM <= 65535 && (long long)n_groups * N < (1LL << 31), "gemm_tc_grouped: too many rows");
+  const int bn = epilogue == TC_EPI_SWIGLU ? 64 : 128;
+  CUtensorMap ma, mb, mb2;
+  if (tensor_map(a, M, K, lda, TC_BM, &ma)) return -1;
+  if (tensor_map(w, n_groups * N, K, K, bn, &mb)) return -1;
+  mb2 = mb;
+  if (w2 && tensor_map(w2, n_groups * N, K, K, bn, &mb2)) return -1;
+  const size_t esz = out_dtype == DT_F32 ? 4 : 2;
+  const int vec_ok = ((uintptr_t)out % 16 == 0) && ((size_t)ldo * esz % 16 == 0);
+  GroupedTiles grp;
+  grp.tile_group = tile_group;
+  grp.rows_per_group = N;
+  int rc;
+  if (epilogue == TC_EPI_SWIGLU)
+    rc = launch_tc<64, TC_EPI_SWIGLU, __nv_bfloat16>(ma, mb, mb2, out, ldo, nullptr, M, N, K, vec_ok, err, stream, false, RopeAppend{}, grp);
+  else if (out_dtype == DT_F32)
+    rc = launch_tc<128, TC_EPI_STORE, float>(ma, mb, mb2, out, ldo, nullptr, M, N, K, vec_ok, err, stream, false, RopeAppend{}, grp);
+  else
+    rc = launch_tc<128, TC_EPI_STORE, __nv_bfloat16>(ma, mb, mb2, out, ldo, nullptr, M, N, K, vec_ok, err, stream, false, RopeAppend{}, grp);
+  if (rc) return rc;
+  EL_LAUNCH_CHECK("gemm_tc_grouped");
+  return 0;
 }
 
 // 1 if the stacked q, k, v projection of a prompt step can rotate and append in its epilogue: bfloat16, head size 64

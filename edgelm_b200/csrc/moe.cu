@@ -4,9 +4,11 @@
 //             weights: the softmax over the chosen logits only.
 //   plan      the (token, choice) pairs are grouped by expert: rows of a padded layout in which every expert's rows
 //             start at a multiple of the row tile, so that a tile of rows belongs to one expert.
-//             row_pair[row] = pair (token * top + choice) or -1; tile_expert[tile] = expert or -1.
-//   products  mid[row] = silu(Wg_e h) * (Wu_e h) for the row's token; y[pair] = Wd_e mid[row] (float32).
-//   combine   x[t] += sum_k weight[t][k] * y[t * top + k], in the order of k.
+//             row_pair[row] = pair (token * top + choice) or -1; pair_row[pair] = its row; tile_expert[tile] = expert or -1.
+//   products  mid[row] = silu(Wg_e h) * (Wu_e h) for the row's token; y[row] = Wd_e mid[row] (float32): on the CUDA
+//             cores here (float32 models, sizes the tensor-core kernel does not take), or by the grouped tcgen05 product
+//             over rows gathered by `gather_rows` (row tiles of 128).
+//   combine   x[t] += sum_k weight[t][k] * y[pair_row[t * top + k]], in the order of k.
 // Every row is computed by itself, so a token's result does not depend on what else is in the step.
 #include "common.cuh"
 
@@ -60,7 +62,7 @@ moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const f
 // arrive; no result does, since every row is computed by itself.
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(const int32_t* __restrict__ idx, int n_pairs, int E, int tile_rows, int max_tiles, int32_t* __restrict__ row_pair,
-                int32_t* __restrict__ tile_expert) {
+                int32_t* __restrict__ pair_row, int32_t* __restrict__ tile_expert) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ int counts[MOE_MAX_EXPERTS], offs[MOE_MAX_EXPERTS];
@@ -87,14 +89,31 @@ moe_plan_kernel(const int32_t* __restrict__ idx, int n_pairs, int E, int tile_ro
     const int e = idx[i];
     if (e >= 0 && e < E) {
       const int r = offs[e] + atomicAdd(&counts[e], 1);
-      if (r < max_tiles * tile_rows) row_pair[r] = i;
+      if (r < max_tiles * tile_rows) { row_pair[r] = i; pair_row[i] = r; }
+    } else {
+      pair_row[i] = -1;
     }
   }
 }
 
+// a[row][:] = h[row_pair[row] / top][:], zeros for a row of no pair: the grouped rows as a matrix of their own
+template <typename T>
+__global__ void moe_gather_rows_kernel(const T* __restrict__ h, T* __restrict__ a, const int32_t* __restrict__ row_pair, int top, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, p = row_pair[r];
+  T* dst = a + (size_t)r * D;
+  if (p < 0) {
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = from_f32<T>(0.f);
+    return;
+  }
+  const T* src = h + (size_t)(p / top) * D;
+  for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+}
+
 // The products on the CUDA cores (float32 sums): tiles of 32 rows x 64 columns, K in steps of 32 through shared memory.
 //   GATED: a[row] = h[row_pair[row] / top]; out[row][n] = silu(a . wg_e[n]) * (a . wu_e[n])          (mid, type T)
-//   else:  a[row] = mid[row];               y[row_pair[row]][n] = a . w_e[n]                          (float32)
+//   else:  a[row] = mid[row];               y[row][n] = a . w_e[n]                                    (float32)
 constexpr int MG_TM = 32, MG_TN = 64, MG_KC = 32;
 
 template <typename T, bool GATED>
@@ -160,20 +179,24 @@ moe_gemm_kernel(const T* __restrict__ a, int lda, const T* __restrict__ w, const
         const float z = acc[i][j];
         ((T*)out)[(size_t)(r0 + r) * ldo + n] = from_f32<T>(z / (1.0f + expf(-z)) * acc2[i][j]);
       } else {
-        ((float*)out)[(size_t)p * ldo + n] = acc[i][j];
+        ((float*)out)[(size_t)(r0 + r) * ldo + n] = acc[i][j];
       }
     }
   }
 }
 
-// x[t][:] += sum_k wts[t][k] * y[t * top + k][:]
-__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wts, int top, int D) {
+// x[t][:] += sum_k wts[t][k] * y[pair_row[t * top + k]][:]
+__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ y, int ldy, const float* __restrict__ wts,
+                                   const int32_t* __restrict__ pair_row, int top, int D) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < D; i += blockDim.x) {
     float acc = 0.f;
-    for (int k = 0; k < top; ++k) acc = fmaf(wts[(size_t)t * top + k], y[((size_t)t * top + k) * D + i], acc);
+    for (int k = 0; k < top; ++k) {
+      const int r = pair_row[(size_t)t * top + k];
+      if (r >= 0) acc = fmaf(wts[(size_t)t * top + k], y[(size_t)r * ldy + i], acc);
+    }
     x[(size_t)t * D + i] += acc;
   }
 }
@@ -199,18 +222,18 @@ extern "C" int edgelm_moe_route(const void* h, int dtype, const float* wr, const
   return 0;
 }
 
-extern "C" int edgelm_moe_plan(const int32_t* idx, int n_pairs, int E, int tile_rows, int max_tiles, int32_t* row_pair, int32_t* tile_expert,
-                               cudaStream_t stream) {
+extern "C" int edgelm_moe_plan(const int32_t* idx, int n_pairs, int E, int tile_rows, int max_tiles, int32_t* row_pair, int32_t* pair_row,
+                               int32_t* tile_expert, cudaStream_t stream) {
   if (n_pairs == 0) return 0;
   EL_REFUSE(n_pairs > 0 && E >= 1 && E <= MOE_MAX_EXPERTS && tile_rows >= 1, "moe_plan: bad sizes");
   EL_REFUSE(max_tiles >= n_pairs / tile_rows + E || max_tiles >= n_pairs, "moe_plan: %d tiles of %d rows cannot hold %d pairs of %d experts", max_tiles, tile_rows, n_pairs, E);
-  launch_pdl(pdl_bit_for_tokens(n_pairs), moe_plan_kernel, dim3(1), dim3(1024), (size_t)0, stream, idx, n_pairs, E, tile_rows, max_tiles, row_pair, tile_expert);
+  launch_pdl(pdl_bit_for_tokens(n_pairs), moe_plan_kernel, dim3(1), dim3(1024), (size_t)0, stream, idx, n_pairs, E, tile_rows, max_tiles, row_pair, pair_row, tile_expert);
   EL_LAUNCH_CHECK("moe_plan");
   return 0;
 }
 
 // gated != 0: the gate and up products with the activation; a = the tokens' rows [tokens][K]; out = mid [rows][N] in `dtype`.
-// gated == 0: the down product; a = mid [rows][K]; out = y [pairs][N] float32.
+// gated == 0: the down product; a = mid [rows][K]; out = y [rows][N] float32.
 extern "C" int edgelm_moe_gemm(const void* a, int lda, const void* w, const void* w2, void* out, int ldo, const int32_t* row_pair,
                                const int32_t* tile_expert, int max_tiles, int top, int K, int N, int dtype, int gated, cudaStream_t stream) {
   if (max_tiles == 0) return 0;
@@ -228,10 +251,22 @@ extern "C" int edgelm_moe_gemm(const void* a, int lda, const void* w, const void
   return 0;
 }
 
-extern "C" int edgelm_moe_combine(float* x, const float* y, const float* wts, int n_tokens, int top, int D, cudaStream_t stream) {
+extern "C" int edgelm_moe_gather_rows(const void* h, void* a, const int32_t* row_pair, int n_rows, int top, int D, int dtype, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  EL_REFUSE(n_rows > 0 && top >= 1 && D > 0, "moe_gather_rows: bad sizes");
+  const dim3 grid(n_rows), block(D >= 1024 ? 256 : 128);
+  if (dtype == DT_F32) launch_pdl(pdl_bit_for_tokens(n_rows), moe_gather_rows_kernel<float>, grid, block, (size_t)0, stream, (const float*)h, (float*)a, row_pair, top, D);
+  else if (dtype == DT_BF16) launch_pdl(pdl_bit_for_tokens(n_rows), moe_gather_rows_kernel<__nv_bfloat16>, grid, block, (size_t)0, stream, (const __nv_bfloat16*)h, (__nv_bfloat16*)a, row_pair, top, D);
+  else EL_REFUSE(false, "moe_gather_rows: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("moe_gather_rows");
+  return 0;
+}
+
+extern "C" int edgelm_moe_combine(float* x, const float* y, int ldy, const float* wts, const int32_t* pair_row, int n_tokens, int top, int D,
+                                  cudaStream_t stream) {
   if (n_tokens == 0) return 0;
-  EL_REFUSE(n_tokens > 0 && top >= 1 && D > 0, "moe_combine: bad sizes");
-  launch_pdl(pdl_bit_for_tokens(n_tokens), moe_combine_kernel, dim3(n_tokens), dim3(D >= 1024 ? 256 : 128), (size_t)0, stream, x, y, wts, top, D);
+  EL_REFUSE(n_tokens > 0 && top >= 1 && D > 0 && ldy >= D, "moe_combine: bad sizes");
+  launch_pdl(pdl_bit_for_tokens(n_tokens), moe_combine_kernel, dim3(n_tokens), dim3(D >= 1024 ? 256 : 128), (size_t)0, stream, x, y, ldy, wts, pair_row, top, D);
   EL_LAUNCH_CHECK("moe_combine");
   return 0;
 }

@@ -756,9 +756,10 @@ def delta_scan(qkv, bg, state, o, seq_tok0, seq_slot, n_seqs, heads, kv_heads, d
 
 
 # ----------------------------------------------------------------------------- mixture of experts
-def moe_tile_rows():
-    """Rows of a tile of the grouped products: every expert's rows start at a multiple of it."""
-    return int(lib().edgelm_moe_tile_rows())
+def moe_tile_rows(tensor_cores=False):
+    """Rows of a tile of the grouped products: every expert's rows start at a multiple of it (the CUDA-core kernels'
+    tile, or the tcgen05 kernel's 128)."""
+    return 128 if tensor_cores else int(lib().edgelm_moe_tile_rows())
 
 
 def moe_max_tiles(n_pairs, n_experts, tile_rows):
@@ -776,35 +777,65 @@ def moe_route(h, wr, br, idx, wts, top):
     _check(lib().edgelm_moe_route(_p(h), _dt(h), _p(wr), _p(br), _p(idx), _p(wts), T, D, E, int(top), _stream()))
 
 
-def moe_plan(idx, n_experts, tile_rows, row_pair, tile_expert):
-    """Group the pairs of idx [T, top] by expert: row_pair [max_tiles * tile_rows] (pair or -1), tile_expert [max_tiles]."""
-    _i32(idx, "idx"); _i32(row_pair, "row_pair"); _i32(tile_expert, "tile_expert")
+def moe_plan(idx, n_experts, tile_rows, row_pair, pair_row, tile_expert):
+    """Group the pairs of idx [T, top] by expert: row_pair [max_tiles * tile_rows] (pair or -1), pair_row [T * top] (each
+    pair's row), tile_expert [max_tiles] (the expert of a tile of rows, or -1)."""
+    _i32(idx, "idx"); _i32(row_pair, "row_pair"); _i32(pair_row, "pair_row"); _i32(tile_expert, "tile_expert")
     max_tiles = tile_expert.numel()
-    _need(row_pair.numel() == max_tiles * tile_rows, "moe_plan: row_pair size")
-    _check(lib().edgelm_moe_plan(_p(idx), idx.numel(), int(n_experts), int(tile_rows), max_tiles, _p(row_pair), _p(tile_expert), _stream()))
+    _need(row_pair.numel() == max_tiles * tile_rows and pair_row.numel() == idx.numel(), "moe_plan: sizes of the maps")
+    _check(lib().edgelm_moe_plan(_p(idx), idx.numel(), int(n_experts), int(tile_rows), max_tiles, _p(row_pair), _p(pair_row), _p(tile_expert), _stream()))
+
+
+def moe_gather_rows(h, a, row_pair, top):
+    """a[row] = h[row_pair[row] // top], zeros for a row without a pair."""
+    _i32(row_pair, "row_pair")
+    _need(h.dtype == a.dtype and h.is_contiguous() and a.is_contiguous() and a.shape == (row_pair.numel(), h.shape[1]), "moe_gather_rows: shapes")
+    _check(lib().edgelm_moe_gather_rows(_p(h), _p(a), _p(row_pair), row_pair.numel(), int(top), h.shape[1], _dt(h), _stream()))
 
 
 def moe_gate_up(h, w_gate, w_up, mid, row_pair, tile_expert, top):
-    """mid[row] = silu(w_gate[e] h[t]) * (w_up[e] h[t]) for every row of the plan (t = row_pair[row] // top, e the row's tile's expert)."""
+    """mid[row] = silu(w_gate[e] h[t]) * (w_up[e] h[t]) for every row of the plan (t = row_pair[row] // top, e the row's tile's
+    expert), on the CUDA cores."""
     E, N, K = w_gate.shape
     _need(h.dtype == w_gate.dtype == w_up.dtype == mid.dtype and h.is_contiguous() and w_gate.is_contiguous() and w_up.is_contiguous() and mid.is_contiguous(), "moe_gate_up: layout")
     _need(h.shape[1] == K and w_up.shape == w_gate.shape and mid.shape == (row_pair.numel(), N), "moe_gate_up: shapes")
+    _need(row_pair.numel() == tile_expert.numel() * moe_tile_rows(), "moe_gate_up: the plan's row tile is not this kernel's")
     _check(lib().edgelm_moe_gemm(_p(h), h.stride(0), _p(w_gate), _p(w_up), _p(mid), mid.stride(0), _p(row_pair), _p(tile_expert),
                                  tile_expert.numel(), int(top), K, N, _dt(h), 1, _stream()))
 
 
 def moe_down(mid, w_down, y, row_pair, tile_expert, top):
-    """y[pair] = w_down[e] mid[row] (float32) for every row of the plan."""
+    """y[row] = w_down[e] mid[row] (float32) for every row of the plan, on the CUDA cores."""
     E, N, K = w_down.shape
     _f32(y, "y")
-    _need(mid.dtype == w_down.dtype and mid.is_contiguous() and w_down.is_contiguous() and mid.shape == (row_pair.numel(), K) and y.shape[1] == N, "moe_down: shapes")
+    _need(mid.dtype == w_down.dtype and mid.is_contiguous() and w_down.is_contiguous() and mid.shape == (row_pair.numel(), K) and y.shape == (row_pair.numel(), N), "moe_down: shapes")
+    _need(row_pair.numel() == tile_expert.numel() * moe_tile_rows(), "moe_down: the plan's row tile is not this kernel's")
     _check(lib().edgelm_moe_gemm(_p(mid), mid.stride(0), _p(w_down), _p(None), _p(y), y.stride(0), _p(row_pair), _p(tile_expert),
                                  tile_expert.numel(), int(top), K, N, _dt(mid), 0, _stream()))
 
 
-def moe_combine(x, y, wts):
-    """x[t] += sum_k wts[t, k] * y[t * top + k]."""
-    _f32(x, "x"); _f32(y, "y"); _f32(wts, "wts")
+def gemm_tc_grouped_takes(a, w, w2=None):
+    """Whether the grouped tcgen05 product takes these operands: bfloat16, K a multiple of 8, 16-byte aligned rows."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or a.stride(1) != 1:
+        return False
+    return bool(lib().edgelm_gemm_tc_takes(_p(a), a.stride(0), _p(w), _p(w2), a.shape[1]))
+
+
+def gemm_tc_grouped(a, w, out, tile_group, err, epilogue=EPI_STORE, w2=None):
+    """out[row] = a[row] @ w[g].T (+ epilogue) with g = tile_group[row // 128] (negative: a tile without rows): a [M, K]
+    bfloat16 with M a multiple of 128, w (and w2 for SwiGLU) [groups, N, K] bfloat16, out [M, N] float32 or bfloat16."""
+    _i32(tile_group, "tile_group")
+    G, N, K = w.shape
+    M = a.shape[0]
+    _need(a.shape == (M, K) and out.shape == (M, N) and out.stride(1) == 1 and tile_group.numel() * 128 == M, "gemm_tc_grouped: shapes")
+    _need(w2 is None or (w2.shape == w.shape and w2.is_contiguous() and w2.dtype == w.dtype), "gemm_tc_grouped: second weight")
+    _check(lib().edgelm_gemm_tc_grouped(_p(a), a.stride(0), _p(w), _p(w2), _p(out), out.stride(0), M, N, K, G, _p(tile_group), _dt(out), int(epilogue),
+                                        _p(err), _stream()))
+
+
+def moe_combine(x, y, wts, pair_row):
+    """x[t] += sum_k wts[t, k] * y[pair_row[t * top + k]]."""
+    _f32(x, "x"); _f32(y, "y"); _f32(wts, "wts"); _i32(pair_row, "pair_row")
     T, top = wts.shape
-    _need(x.shape[0] == T and y.shape == (T * top, x.shape[1]), "moe_combine: shapes")
-    _check(lib().edgelm_moe_combine(_p(x), _p(y), _p(wts), T, top, x.shape[1], _stream()))
+    _need(x.shape[0] == T and y.shape[1] == x.shape[1] and pair_row.numel() == T * top, "moe_combine: shapes")
+    _check(lib().edgelm_moe_combine(_p(x), _p(y), y.stride(0), _p(wts), _p(pair_row), T, top, x.shape[1], _stream()))

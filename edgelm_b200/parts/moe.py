@@ -57,15 +57,21 @@ class MixtureOfExperts(Part):
         self.w_router = as_matrix(tensors[prefix + n["router"]], torch.float32, device)
         self.b_router = as_vector(tensors[prefix + n["router_bias"]], device)
 
-    def _max_tiles(self, n_tokens):
-        return ops.moe_max_tiles(n_tokens * self.top, self.n_experts, ops.moe_tile_rows())
+    def _on_tensor_cores(self):
+        """Whether the experts' products run as grouped tcgen05 products (bfloat16 and sizes that kernel takes)."""
+        return (self.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0 and self.w_gate is not None and
+                self.w_gate.data_ptr() % 16 == 0 and self.w_up.data_ptr() % 16 == 0 and self.w_down.data_ptr() % 16 == 0)
+
+    def _max_tiles(self, n_tokens, tile_rows):
+        return ops.moe_max_tiles(n_tokens * self.top, self.n_experts, tile_rows)
 
     def workspace_bytes(self, n_tokens, n_seqs):
-        rows = self._max_tiles(n_tokens) * ops.moe_tile_rows()
-        pairs = n_tokens * self.top
-        return (nbytes((n_tokens, self.hidden), self.dtype) + nbytes((pairs,), torch.int32) + nbytes((pairs,), torch.float32) +
-                nbytes((rows,), torch.int32) + nbytes((self._max_tiles(n_tokens),), torch.int32) + nbytes((rows, self.inter), self.dtype) +
-                nbytes((pairs, self.hidden), torch.float32))
+        tile_rows = ops.moe_tile_rows(self._on_tensor_cores())
+        tiles = self._max_tiles(n_tokens, tile_rows)
+        rows, pairs = tiles * tile_rows, n_tokens * self.top
+        return (nbytes((n_tokens, self.hidden), self.dtype) + 2 * nbytes((pairs,), torch.int32) + nbytes((pairs,), torch.float32) +
+                nbytes((rows,), torch.int32) + nbytes((tiles,), torch.int32) + nbytes((rows, self.hidden), self.dtype) +
+                nbytes((rows, self.inter), self.dtype) + nbytes((rows, self.hidden), torch.float32))
 
     def first_weights(self):
         return ()
@@ -73,21 +79,34 @@ class MixtureOfExperts(Part):
     def forward(self, ctx, h, x, accumulate=True):
         h = linear.as_tensor(h)
         T, ws = h.shape[0], ctx.ws
-        tile_rows, max_tiles = ops.moe_tile_rows(), self._max_tiles(T)
+        tc = self._on_tensor_cores()
+        tile_rows = ops.moe_tile_rows(tc)
+        max_tiles = self._max_tiles(T, tile_rows)
+        rows = max_tiles * tile_rows
         idx = ws.alloc((T, self.top), torch.int32)
         wts = ws.alloc((T, self.top), torch.float32)
-        row_pair = ws.alloc((max_tiles * tile_rows,), torch.int32)
+        row_pair = ws.alloc((rows,), torch.int32)
+        pair_row = ws.alloc((T * self.top,), torch.int32)
         tile_expert = ws.alloc((max_tiles,), torch.int32)
         with ctx.prof("moe_route"):
             ops.moe_route(h, self.w_router, self.b_router, idx, wts, self.top)
-            ops.moe_plan(idx, self.n_experts, tile_rows, row_pair, tile_expert)
-        mid = ws.alloc((max_tiles * tile_rows, self.inter), self.dtype)
-        with ctx.prof("moe_gate_up"):
-            ops.moe_gate_up(h, self.w_gate, self.w_up, mid, row_pair, tile_expert, self.top)
-        y = ws.alloc((T * self.top, self.hidden), torch.float32)
-        with ctx.prof("moe_down"):
-            ops.moe_down(mid, self.w_down, y, row_pair, tile_expert, self.top)
+            ops.moe_plan(idx, self.n_experts, tile_rows, row_pair, pair_row, tile_expert)
+        mid = ws.alloc((rows, self.inter), self.dtype)
+        y = ws.alloc((rows, self.hidden), torch.float32)
+        if tc:
+            a = ws.alloc((rows, self.hidden), self.dtype)
+            with ctx.prof("moe_gather"):
+                ops.moe_gather_rows(h, a, row_pair, self.top)
+            with ctx.prof("moe_gate_up"):
+                ops.gemm_tc_grouped(a, self.w_gate, mid, tile_expert, ctx.err, epilogue=linear.EPI_SWIGLU, w2=self.w_up)
+            with ctx.prof("moe_down"):
+                ops.gemm_tc_grouped(mid, self.w_down, y, tile_expert, ctx.err)
+        else:
+            with ctx.prof("moe_gate_up"):
+                ops.moe_gate_up(h, self.w_gate, self.w_up, mid, row_pair, tile_expert, self.top)
+            with ctx.prof("moe_down"):
+                ops.moe_down(mid, self.w_down, y, row_pair, tile_expert, self.top)
         with ctx.prof("moe_combine"):
             if not accumulate:
                 x.zero_()
-            ops.moe_combine(x, y, wts)
+            ops.moe_combine(x, y, wts, pair_row)

@@ -23,7 +23,27 @@ def _sagizen(vocab, width, ff, groups_of_layers, ssm_heads, ssm_state, heads, kv
             "layers": [ssm, ssm, ssm, par] * groups_of_layers}
 
 
+def _vosulorn(vocab, width, ff, groups_of_layers, heads, kv_heads, kv_rank, rot_dim, chunk, experts, top):
+    """A Vosulorn-shaped model: per group a delta-rule layer, a latent-attention layer, a second delta-rule layer and a
+    layer of chunked attention with a sink, heads of 64 everywhere, every layer with a mixture of `experts` experts of which
+    a token uses `top` (so `top * ff` is the feed-forward width a token sees)."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    delta = {"type": "delta", "mlp": moe, "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4}}
+    latent = {"type": "latent_attention", "mlp": moe, "mixer": {
+        "heads": heads, "dim": 64, "rot_dim": rot_dim, "vdim": 64, "kv_rank": kv_rank, "scale": (64 + rot_dim) ** -0.5,
+        "rot": {"base": 500000.0, "dims": rot_dim}}}
+    attn = {"type": "attention", "mlp": moe, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": chunk},
+        "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}}
+    return {"architecture": "Vosulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "max_positions": 8192, "layers": [delta, latent, delta, attn] * groups_of_layers}
+
+
 PRESETS = {
+    # the layer sizes of smollm2-135m and smollm2-1.7b (width, heads of 64, vocabulary; a token's two experts together as
+    # wide as the dense feed-forward) in the Vosulorn design
+    "vosulorn-576": _vosulorn(49152, 576, 768, 2, 9, 3, 128, 32, 1024, 8, 2),
+    "vosulorn-2048": _vosulorn(49152, 2048, 4096, 1, 32, 32, 512, 64, 1024, 8, 2),
     # the layer sizes of smollm2-135m and smollm2-1.7b (width, feed-forward, heads of 64, vocabulary) in the Sagizen design
     "sagizen-576": _sagizen(49152, 576, 1536, 2, 18, 128, 9, 3, 512, 64),
     "sagizen-2048": _sagizen(49152, 2048, 8192, 1, 64, 128, 32, 32, 1024, 64),
