@@ -16,7 +16,8 @@
 // pairs, cache append); `latent_prepare` (rotation of the queries' rotated part; RMS norm of the latent, rotation of
 // the shared key part, cache append); `head_matmul` (one small matrix product per head: queries into the latent's
 // space, weighted latents out of it); `masked_attn` (a block per token and head: steps of one token a sequence);
-// `masked_attn_tiled` (prompt steps: keys staged once for 32 rows); `add_row_bias`.
+// `masked_attn_tiled` (prompt steps: keys staged once for 32 rows, from the cache's pages or from the step's own rows);
+// `latent_expand_keys`; `add_row_bias`.
 #include "common.cuh"
 
 namespace edgelm {
@@ -98,15 +99,17 @@ rotate_append_kernel(const float* __restrict__ qkv, const float* __restrict__ bi
 }
 
 // u [tokens][ldu] float32: H query heads of [d | rd] from column 0 and, with `has_kv`, the latent's row [r | rd] from
-// column kv_off.  The rotated part of every query head (half-split pairs) goes to q_full[t][h][r + i]; the latent,
-// divided by its root mean square and times `norm_w`, and the rotated shared key part become the token's cache row
-// [r + rd] (one key head).
+// column kv_off.  The rotated part of every query head (half-split pairs) goes to q_out[t][h * q_pitch + q_off + i], and with
+// `copy_q` the unrotated part to q_out[t][h * q_pitch + i]; the latent, divided by its root mean square and times `norm_w`,
+// and the rotated shared key part become the token's cache row [r + rd] (one key head) and, if `row_out` is given, row t
+// of it as well (what the cache holds, for a step that expands its own keys).
 template <typename T>
 __global__ void __launch_bounds__(256)
-latent_prepare_kernel(const float* __restrict__ u, int ldu, int kv_off, int has_kv, float* __restrict__ q_full,
-                      const float* __restrict__ norm_w, float eps, const int32_t* __restrict__ tok_pos,
+latent_prepare_kernel(const float* __restrict__ u, int ldu, int kv_off, int has_kv, float* __restrict__ q_out, int q_pitch, int q_off,
+                      int copy_q, const float* __restrict__ norm_w, float eps, const int32_t* __restrict__ tok_pos,
                       const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ page_table, int table_stride, int n_pages,
-                      T* __restrict__ kcache, int H, int d, int rd, int r, const double* __restrict__ freq, int* __restrict__ err) {
+                      T* __restrict__ kcache, T* __restrict__ row_out, int H, int d, int rd, int r, const double* __restrict__ freq,
+                      int* __restrict__ err) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[33];
@@ -117,10 +120,16 @@ latent_prepare_kernel(const float* __restrict__ u, int ldu, int kv_off, int has_
     return;
   }
   const float* row = u + (size_t)t * ldu;
+  float* qo = q_out + (size_t)t * H * q_pitch;
   for (int i = threadIdx.x; i < H * rd; i += blockDim.x) {
     const int h = i / rd, j = i - h * rd;
-    q_full[((size_t)t * H + h) * (r + rd) + r + j] = rotated(row + (size_t)h * (d + rd) + d, j, rd, 0, (double)pos, freq);
+    qo[(size_t)h * q_pitch + q_off + j] = rotated(row + (size_t)h * (d + rd) + d, j, rd, 0, (double)pos, freq);
   }
+  if (copy_q)
+    for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+      const int h = i / d, j = i - h * d;
+      qo[(size_t)h * q_pitch + j] = row[(size_t)h * (d + rd) + j];
+    }
   if (!has_kv) return;
   const int page = page_table[(size_t)tok_seq[t] * table_stride + pos / PAGE];
   if (page < 0 || page >= n_pages) {
@@ -133,8 +142,25 @@ latent_prepare_kernel(const float* __restrict__ u, int ldu, int kv_off, int has_
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)r + eps);
   T* dst = kcache + ((size_t)page * PAGE + pos % PAGE) * (r + rd);
-  for (int i = threadIdx.x; i < r; i += blockDim.x) dst[i] = from_f32<T>(c[i] * inv * norm_w[i]);
-  for (int i = threadIdx.x; i < rd; i += blockDim.x) dst[r + i] = from_f32<T>(rotated(c + r, i, rd, 0, (double)pos, freq));
+  T* dst2 = row_out ? row_out + (size_t)t * (r + rd) : nullptr;
+  for (int i = threadIdx.x; i < r + rd; i += blockDim.x) {
+    const T v = from_f32<T>(i < r ? c[i] * inv * norm_w[i] : rotated(c + r, i - r, rd, 0, (double)pos, freq));
+    dst[i] = v;
+    if (dst2) dst2[i] = v;
+  }
+}
+
+// kx[t][h][:] = [kn[t][h][0 .. d) | row[t][r .. r + rd)]: a step's keys per head, the shared rotated part repeated
+template <typename T>
+__global__ void latent_expand_keys_kernel(const T* __restrict__ kn, const T* __restrict__ rows, T* __restrict__ kx, int H, int d, int rd, int r) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const T* shared_part = rows + (size_t)t * (r + rd) + r;
+  for (int i = threadIdx.x; i < H * (d + rd); i += blockDim.x) {
+    const int h = i / (d + rd), j = i - h * (d + rd);
+    kx[(size_t)t * H * (d + rd) + i] = j < d ? kn[((size_t)t * H + h) * d + j] : shared_part[j - d];
+  }
 }
 
 // out[t][h * out_hs + n] = sum_k a[t][h * a_hs + k] * w[h][n][k], float32 sums; a: float32 rows of lda floats, out: rows of ldo values.
@@ -332,7 +358,11 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
   const int tile = blockIdx.x, g = blockIdx.y, grp = H / G;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int seq = tile_seq[tile], tok0 = tile_tok0[tile], ntok = tile_ntok[tile], pos0 = tile_pos0[tile];
-  const int32_t* pages = page_table + (size_t)seq * table_stride;
+  // `page_table` null: the keys and values are the step's own rows [token][kv_head][dk or dv] (every sequence of the step
+  // starts at position 0, so position p of the tile's sequence is packed row tok0 - pos0 + p)
+  const bool paged = page_table != nullptr;
+  const int32_t* pages = paged ? page_table + (size_t)seq * table_stride : nullptr;
+  const int k_pitch = paged ? dk : G * dk, v_pitch = paged ? dv : G * dv;
   const int rows_total = ntok * grp, row_base = blockIdx.z * TM_ROWS;
   if (row_base >= rows_total) return;
   const int rows_here = min(TM_ROWS, rows_total - row_base);
@@ -356,18 +386,22 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
   }
   const int kt_begin = first_key(first_pos, mask, mask_size) / PAGE, kt_end = last_pos / PAGE;
   for (int kt = kt_begin; kt <= kt_end; ++kt) {
-    const int page = pages[kt];
-    const bool held = page >= 0 && page < n_pages;
-    const T* kp = kcache + ((size_t)(held ? page : 0) * G + g) * PAGE * dk;
+    const int page = paged ? pages[kt] : 0;
+    const bool held = !paged || (page >= 0 && page < n_pages);
+    const size_t first_row = paged ? ((size_t)(held ? page : 0) * G + g) * PAGE : ((size_t)(tok0 - pos0 + kt * PAGE) * G + g);
+    const T* kp = kcache + first_row * dk;
     const int valid = held ? min(PAGE, last_pos + 1 - kt * PAGE) : 0;   // rows of the page that hold this block's keys
     __syncthreads();
     for (int i = threadIdx.x; i < PAGE * dk; i += blockDim.x) {
       const int j = i / dk, d = i - j * dk;
-      Ks[j * ks + d] = j < valid ? to_f32(kp[i]) : 0.f;   // what lies behind is not this sequence's: never let it in
+      Ks[j * ks + d] = j < valid ? to_f32(kp[(size_t)j * k_pitch + d]) : 0.f;   // what lies behind is not this sequence's: never let it in
     }
     if (own_v) {
-      const T* vp = vcache + ((size_t)(held ? page : 0) * G + g) * PAGE * dv;
-      for (int i = threadIdx.x; i < PAGE * dv; i += blockDim.x) Vs[i] = i / dv < valid ? to_f32(vp[i]) : 0.f;
+      const T* vp = vcache + first_row * dv;
+      for (int i = threadIdx.x; i < PAGE * dv; i += blockDim.x) {
+        const int j = i / dv, d = i - j * dv;
+        Vs[i] = j < valid ? to_f32(vp[(size_t)j * v_pitch + d]) : 0.f;
+      }
     }
     __syncthreads();
     const int base = kt * PAGE;
@@ -477,24 +511,41 @@ extern "C" int edgelm_rotate_append(const float* qkv, const float* bias, float* 
   return 0;
 }
 
-extern "C" int edgelm_latent_prepare(const float* u, int ldu, int kv_off, int has_kv, float* q_full, const float* norm_w, float eps,
-                                     const int32_t* tok_pos, const int32_t* tok_seq, const int32_t* page_table, int table_stride,
-                                     int n_pages, void* kcache, int dtype, int n_tokens, int H, int d, int rd, int r, const double* freq,
-                                     int* err, cudaStream_t stream) {
+extern "C" int edgelm_latent_prepare(const float* u, int ldu, int kv_off, int has_kv, float* q_out, int q_pitch, int q_off, int copy_q,
+                                     const float* norm_w, float eps, const int32_t* tok_pos, const int32_t* tok_seq,
+                                     const int32_t* page_table, int table_stride, int n_pages, void* kcache, void* row_out, int dtype,
+                                     int n_tokens, int H, int d, int rd, int r, const double* freq, int* err, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && H > 0 && d >= 0 && r >= 1 && rd >= 0 && rd % 2 == 0, "latent_prepare: sizes heads %d, %d + %d, latent %d", H, d, rd, r);
   EL_REFUSE(rd == 0 || freq != nullptr, "latent_prepare: no frequencies");
   EL_REFUSE(H * (d + rd) <= ldu && (!has_kv || kv_off + r + rd <= ldu), "latent_prepare: rows of %d values are too short", ldu);
+  EL_REFUSE(q_off >= (copy_q ? d : 0) && q_off + rd <= q_pitch, "latent_prepare: a query head of %d values does not hold %d at %d", q_pitch, rd, q_off);
   const int bit = pdl_bit_for_tokens(n_tokens);
   if (dtype == DT_F32)
-    launch_pdl(bit, latent_prepare_kernel<float>, dim3(n_tokens), dim3(256), (size_t)0, stream, u, ldu, kv_off, has_kv, q_full, norm_w, eps,
-               tok_pos, tok_seq, page_table, table_stride, n_pages, (float*)kcache, H, d, rd, r, freq, err);
+    launch_pdl(bit, latent_prepare_kernel<float>, dim3(n_tokens), dim3(256), (size_t)0, stream, u, ldu, kv_off, has_kv, q_out, q_pitch, q_off, copy_q,
+               norm_w, eps, tok_pos, tok_seq, page_table, table_stride, n_pages, (float*)kcache, (float*)row_out, H, d, rd, r, freq, err);
   else if (dtype == DT_BF16)
-    launch_pdl(bit, latent_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), (size_t)0, stream, u, ldu, kv_off, has_kv, q_full, norm_w,
-               eps, tok_pos, tok_seq, page_table, table_stride, n_pages, (__nv_bfloat16*)kcache, H, d, rd, r, freq, err);
+    launch_pdl(bit, latent_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), (size_t)0, stream, u, ldu, kv_off, has_kv, q_out, q_pitch, q_off,
+               copy_q, norm_w, eps, tok_pos, tok_seq, page_table, table_stride, n_pages, (__nv_bfloat16*)kcache, (__nv_bfloat16*)row_out, H, d, rd,
+               r, freq, err);
   else
     EL_REFUSE(false, "latent_prepare: unknown dtype code %d", dtype);
   EL_LAUNCH_CHECK("latent_prepare");
+  return 0;
+}
+
+extern "C" int edgelm_latent_expand_keys(const void* kn, const void* rows, void* kx, int dtype, int n_tokens, int H, int d, int rd, int r,
+                                         cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  EL_REFUSE(n_tokens > 0 && H > 0 && d >= 0 && rd >= 0 && d + rd >= 1 && r >= 1, "latent_expand_keys: bad sizes");
+  if (dtype == DT_F32)
+    launch_pdl(0, latent_expand_keys_kernel<float>, dim3(n_tokens), dim3(256), (size_t)0, stream, (const float*)kn, (const float*)rows, (float*)kx, H, d, rd, r);
+  else if (dtype == DT_BF16)
+    launch_pdl(0, latent_expand_keys_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), (size_t)0, stream, (const __nv_bfloat16*)kn,
+               (const __nv_bfloat16*)rows, (__nv_bfloat16*)kx, H, d, rd, r);
+  else
+    EL_REFUSE(false, "latent_expand_keys: unknown dtype code %d", dtype);
+  EL_LAUNCH_CHECK("latent_expand_keys");
   return 0;
 }
 

@@ -1,6 +1,6 @@
 // A feed-forward made of experts, of which every token uses the `top` with the largest router logits.
 //
-//   route     logits z = Wr h + br in float32 (a warp a token); the `top` largest (first maximum on ties), and their
+//   route     logits z = Wr h + br in float32 (a block a token); the `top` largest (first maximum on ties), and their
 //             weights: the softmax over the chosen logits only.
 //   plan      the (token, choice) pairs are grouped by expert: rows of a padded layout in which every expert's rows
 //             start at a multiple of the row tile, so that a tile of rows belongs to one expert.
@@ -16,29 +16,42 @@ namespace edgelm {
 
 constexpr int MOE_MAX_EXPERTS = 1024;
 
+// A block a token: its four warps share the width, eight experts at a time (the token's row is read once for the eight,
+// and a thread has eight independent sums and several steps of loads in flight); the warps' sums are added in a fixed order.
 template <typename TH>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const TH* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ br, int32_t* __restrict__ idx,
                  float* __restrict__ wts, int n_tokens, int D, int E, int top) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float mr_logits[];       // [warps][E]
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
-  const int t = blockIdx.x * NW + warp;
-  if (t >= n_tokens) return;
-  float* z = mr_logits + warp * E;
+  extern __shared__ float mr_smem[];         // [E] logits, then [4][8] partial sums
+  float* z = mr_smem;
+  float* part = mr_smem + E;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x;
   const TH* row = h + (size_t)t * D;
-  for (int e = 0; e < E; ++e) {
-    const float* w = wr + (size_t)e * D;
-    float a0 = 0.f, a1 = 0.f;
-    int i = lane;
-    for (; i + 32 < D; i += 64) { a0 = fmaf(to_f32(row[i]), w[i], a0); a1 = fmaf(to_f32(row[i + 32]), w[i + 32], a1); }
-    if (i < D) a0 = fmaf(to_f32(row[i]), w[i], a0);
-    const float s = warp_sum(a0 + a1);
-    if (lane == 0) z[e] = s + br[e];
+  for (int e0 = 0; e0 < E; e0 += 8) {
+    const float* w[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) w[j] = wr + (size_t)min(e0 + j, E - 1) * D;     // (past the last expert: computed, not kept)
+    float acc[8] = {};
+#pragma unroll 4
+    for (int i = threadIdx.x; i < D; i += 128) {
+      const float x = to_f32(row[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(x, w[j][i], acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sj = warp_sum(acc[j]);
+      if (lane == 0) part[warp * 8 + j] = sj;
+    }
+    __syncthreads();
+    if (threadIdx.x < 8 && e0 + threadIdx.x < E)
+      z[e0 + threadIdx.x] = ((part[threadIdx.x] + part[8 + threadIdx.x]) + (part[16 + threadIdx.x] + part[24 + threadIdx.x])) + br[e0 + threadIdx.x];
+    __syncthreads();
   }
-  __syncwarp();
-  if (lane == 0) {
+  if (threadIdx.x == 0) {
     float zmax = 0.f, sum = 0.f;
     for (int k = 0; k < top; ++k) {
       int best = -1;
@@ -211,9 +224,8 @@ extern "C" int edgelm_moe_route(const void* h, int dtype, const float* wr, const
                                 int E, int top, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && D > 0 && E >= 1 && E <= MOE_MAX_EXPERTS && top >= 1 && top <= E, "moe_route: %d experts, %d chosen", E, top);
-  const int warps = 4;
-  const dim3 grid((n_tokens + warps - 1) / warps), block(warps * 32);
-  const size_t smem = (size_t)warps * E * sizeof(float);
+  const dim3 grid(n_tokens), block(128);
+  const size_t smem = (size_t)(E + 32) * sizeof(float);
   const int bit = pdl_bit_for_tokens(n_tokens);
   if (dtype == DT_F32) launch_pdl(bit, moe_route_kernel<float>, grid, block, smem, stream, (const float*)h, wr, br, idx, wts, n_tokens, D, E, top);
   else if (dtype == DT_BF16) launch_pdl(bit, moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream, (const __nv_bfloat16*)h, wr, br, idx, wts, n_tokens, D, E, top);

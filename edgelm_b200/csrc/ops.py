@@ -659,25 +659,37 @@ def rotate_append(qkv, bias, q_out, tok_pos, tok_seq, page_table, kcache, vcache
                                       1 if interleaved else 0, _p(freq), _p(err), _stream()))
 
 
-def latent_prepare(u, kv_off, has_kv, q_full, norm_w, eps, tok_pos, tok_seq, page_table, kcache, nh, d, rd, r, freq, err):
+def latent_prepare(u, kv_off, has_kv, q_out, q_pitch, q_off, copy_q, norm_w, eps, tok_pos, tok_seq, page_table, kcache, nh, d, rd, r, freq, err,
+                   row_out=None):
     """u [T, *] float32: nh query heads of [d | rd] from column 0 and, with `has_kv`, the latent's row [r | rd] from column
-    `kv_off`.  The rotated part of every query head (pairs (i, i + rd/2)) goes to q_full[t, h, r:]; the latent, RMS-normed
-    with `norm_w`, and the rotated shared key part become the token's cache row [r + rd]."""
-    _f32(u, "u"); _f32(q_full, "q_full")
+    `kv_off`.  The rotated part of every query head (pairs (i, i + rd/2)) goes to q_out[t, h * q_pitch + q_off :], with
+    `copy_q` the unrotated part to q_out[t, h * q_pitch :]; the latent, RMS-normed with `norm_w`, and the rotated shared key
+    part become the token's cache row [r + rd], and row t of `row_out` [T, r + rd] (optional, the cache's type)."""
+    _f32(u, "u"); _f32(q_out, "q_out")
     T = u.shape[0]
-    _need(q_full.shape == (T, nh * (r + rd)), "latent_prepare: q_full shape")
+    _need(q_out.shape == (T, nh * q_pitch), "latent_prepare: q_out shape")
     _need(rd == 0 or (freq is not None and freq.dtype == torch.float64 and freq.numel() == rd // 2 and freq.is_contiguous()), "latent_prepare: frequencies")
     if has_kv:
         _f32(norm_w, "norm_w")
         _need(norm_w.numel() == r, "latent_prepare: the norm's weight")
         _masked_cache_check(kcache, None, 1, r + rd, r, "latent_prepare")
         _i32(page_table, "page_table")
+        _need(row_out is None or (row_out.dtype == kcache.dtype and row_out.is_contiguous() and row_out.shape == (T, r + rd)), "latent_prepare: row_out")
     for t, n in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq")):
         _i32(t, n)
-    _check(lib().edgelm_latent_prepare(_p(u), u.stride(0), int(kv_off), 1 if has_kv else 0, _p(q_full), _p(norm_w) if has_kv else _p(None),
-                                       ctypes.c_float(eps), _p(tok_pos), _p(tok_seq), _p(page_table) if has_kv else _p(None),
-                                       page_table.stride(0) if has_kv else 0, kcache.shape[0] if has_kv else 0,
-                                       _p(kcache) if has_kv else _p(None), _dt(kcache) if has_kv else F32, T, nh, d, rd, r, _p(freq), _p(err), _stream()))
+    _check(lib().edgelm_latent_prepare(_p(u), u.stride(0), int(kv_off), 1 if has_kv else 0, _p(q_out), int(q_pitch), int(q_off), 1 if copy_q else 0,
+                                       _p(norm_w) if has_kv else _p(None), ctypes.c_float(eps), _p(tok_pos), _p(tok_seq),
+                                       _p(page_table) if has_kv else _p(None), page_table.stride(0) if has_kv else 0, kcache.shape[0] if has_kv else 0,
+                                       _p(kcache) if has_kv else _p(None), _p(row_out) if has_kv else _p(None), _dt(kcache) if has_kv else F32,
+                                       T, nh, d, rd, r, _p(freq), _p(err), _stream()))
+
+
+def latent_expand_keys(kn, rows, kx, nh, d, rd, r):
+    """kx[t, h] = [kn[t, h, :d] | rows[t, r:]]: the step's keys per head, the shared rotated part repeated."""
+    T = rows.shape[0]
+    _need(kn.dtype == rows.dtype == kx.dtype and kn.is_contiguous() and rows.is_contiguous() and kx.is_contiguous(), "latent_expand_keys: layout")
+    _need(kn.shape == (T, nh * d) and rows.shape == (T, r + rd) and kx.shape == (T, nh * (d + rd)), "latent_expand_keys: shapes")
+    _check(lib().edgelm_latent_expand_keys(_p(kn), _p(rows), _p(kx), _dt(kx), T, nh, d, rd, r, _stream()))
 
 
 def head_matmul(a, a_head_stride, w, out, out_head_stride):
@@ -718,16 +730,23 @@ def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, d
 def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv,
                       dk, dv, scale, mask, mask_size, sink):
     """`masked_attn` for prompt steps: the step's tokens come as tiles (runs of at most `max_tile_tokens` consecutive tokens of
-    one sequence); a page of keys and values is staged once for all the rows of a tile."""
+    one sequence); a page of keys and values is staged once for all the rows of a tile.  `page_table` None: `kcache` [T, nkv dk]
+    and `vcache` [T, nkv dv] are the step's own keys and values, and every sequence of the step starts at position 0."""
     _f32(q, "q")
     T = q.shape[0]
     _need(q.shape == (T, nh * dk) and out.is_contiguous() and out.shape == (T, nh * dv), "masked_attn_tiled: shapes")
-    _masked_cache_check(kcache, vcache, nkv, dk, dv, "masked_attn_tiled")
+    if page_table is not None:
+        _masked_cache_check(kcache, vcache, nkv, dk, dv, "masked_attn_tiled")
+        _i32(page_table, "page_table")
+    else:
+        _need(vcache is not None and kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == vcache.dtype and
+              kcache.shape == (T, nkv * dk) and vcache.shape == (T, nkv * dv), "masked_attn_tiled: the step's own keys and values")
     _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh), "masked_attn_tiled: sink")
-    for t, n in ((page_table, "page_table"), (tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
+    for t, n in ((tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
         _i32(t, n)
-    _check(lib().edgelm_masked_attn_tiled(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(page_table), page_table.stride(0),
-                                          kcache.shape[0], _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles),
+    _check(lib().edgelm_masked_attn_tiled(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(page_table),
+                                          page_table.stride(0) if page_table is not None else 0, kcache.shape[0] if page_table is not None else 0,
+                                          _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles),
                                           int(max_tile_tokens), nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0), _p(sink), _stream()))
 
 

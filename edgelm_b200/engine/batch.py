@@ -83,6 +83,13 @@ class StepContext:
         """Host list: the absolute position of each sequence's first token of this step."""
         return list(self._seq_pos0)
 
+    @property
+    def all_fresh(self):
+        """Whether every sequence of the step starts at its position 0 (prompts that bring their first tokens): such a
+        step sees no key or state but its own.  A part may take another path then; with `all_single` it is one of the
+        two facts about a step's positions that a captured graph of the step is keyed by."""
+        return not any(self._seq_pos0)
+
     def decode_splits(self, n_kv_heads, resident=None):
         """Blocks per (sequence, kv head) of the decode attention: enough to fill the device, about two an SM.
         `resident`: how many of the kernel's blocks an SM holds at a time, if the caller knows.  With at least as

@@ -8,7 +8,10 @@ W_uk c and the value W_uv c, and score = (q_n . W_uk c + q_r . k_rot) * scale.
 Since q_n . (W_uk c) = (W_uk^T q_n) . c, the queries are moved into the latent's space once per token and attention
 runs over the cache rows [c | k_rot] as they are: one key head of size kv_rank + rot_dim for all query heads, whose first
 kv_rank dimensions are also its value; the weighted latents are then expanded with W_uv.  Nothing per head is ever
-computed for a cached token.  A layer with `reads_cache` keeps nothing: it has no W_dkv and reads the rows that an
+computed for a cached token.  A prompt step whose sequences all start at position 0 (and which keeps its own latent) sees
+only its own tokens: it expands their keys and values per head once, with two matrix products over the rows it has just
+written, and attends over those, heads of head_dim + rot_dim against values of v_head_dim, which is several times fewer
+multiply-adds than rows of the latent's size.  A layer with `reads_cache` keeps nothing: it has no W_dkv and reads the rows that an
 earlier layer of the same kv_rank, rot_dim and rotation left in its cache, with its own W_uk, W_uv, queries and mask.
 
 Angles, the latent's norm, scores, the softmax and the weighted latents are float32 in both precisions; the cache rows
@@ -47,8 +50,10 @@ class LatentAttention(Part):
         self.tile_tokens = max(1, 32 // self.nh)
         self.freq = self.norm_w = None
 
+    EXPANDED_TILE = 32      # tokens a tile when every head has its own keys (a block's 32 rows are 32 tokens of one head)
+
     def tile_sizes(self):
-        return (self.tile_tokens,)
+        return (self.tile_tokens,) if self.reads_foreign_cache else (self.tile_tokens, self.EXPANDED_TILE)
 
     def sizes(self):
         return {"heads": self.nh, "head_dim": self.d, "rot_dim": self.rd, "v_head_dim": self.dv, "kv_rank": self.rank,
@@ -77,9 +82,10 @@ class LatentAttention(Part):
             self.norm_w = as_vector(tensors[prefix + n["dkv_norm"]], device)
         self.w_in = torch.cat(mats, dim=0).contiguous()
         # per head: W_uk^T as [rank, d] (queries into the latent's space) and W_uv as [dv, rank] (weighted latents out of it)
-        uk = as_matrix(tensors[prefix + n["uk"]], self.dtype, device).view(self.nh, self.d, self.rank)
-        self.w_ukt = uk.transpose(1, 2).contiguous()
-        self.w_uv = as_matrix(tensors[prefix + n["uv"]], self.dtype, device).view(self.nh, self.dv, self.rank).contiguous()
+        self.w_uk = as_matrix(tensors[prefix + n["uk"]], self.dtype, device)        # [heads * d, rank]: a step's own keys
+        self.w_ukt = self.w_uk.view(self.nh, self.d, self.rank).transpose(1, 2).contiguous()
+        self.w_uv2 = as_matrix(tensors[prefix + n["uv"]], self.dtype, device)       # [heads * dv, rank]: a step's own values
+        self.w_uv = self.w_uv2.view(self.nh, self.dv, self.rank)
         self.w_o = as_matrix(tensors[prefix + n["o"]], self.dtype, device)
         if self.rd:
             self.freq = rotary_frequencies(self.rd, self.rot_base, self.rot_scaling).to(device).contiguous()
@@ -94,8 +100,36 @@ class LatentAttention(Part):
 
     def workspace_bytes(self, n_tokens, n_seqs):
         f32 = torch.float32
-        return (nbytes((n_tokens, self.d_in), f32) + nbytes((n_tokens, self.nh * self.dc), f32) + nbytes((n_tokens, self.nh * self.rank), f32) +
+        absorbed = nbytes((n_tokens, self.nh * self.dc), f32) + nbytes((n_tokens, self.nh * self.rank), f32)
+        expanded = (nbytes((n_tokens, self.nh * self.dq), f32) + nbytes((n_tokens, self.dc), self.dtype) + nbytes((n_tokens, self.nh * self.d), self.dtype) +
+                    nbytes((n_tokens, self.nh * self.dq), self.dtype) + nbytes((n_tokens, self.nh * self.dv), self.dtype))
+        return (nbytes((n_tokens, self.d_in), f32) + max(absorbed, expanded) +
                 nbytes((n_tokens, self.nh * self.dv), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype))
+
+    def _forward_own_keys(self, ctx, u, x, cache, accumulate):
+        """A prompt step that sees only its own tokens: keys and values expanded per head for the step's tokens."""
+        T, ws = u.shape[0], ctx.ws
+        q = ws.alloc((T, self.nh * self.dq), torch.float32)
+        rows = ws.alloc((T, self.dc), self.dtype)
+        table = ctx.page_table(cache.group)
+        with ctx.prof("latent_prepare"):
+            ops.latent_prepare(u, self.nh * self.dq, True, q, self.dq, self.d, True, self.norm_w, self.eps, ctx.tok_pos, ctx.tok_seq, table,
+                               cache.k, self.nh, self.d, self.rd, self.rank, self.freq, ctx.err, row_out=rows)
+        kn = ws.alloc((T, self.nh * self.d), self.dtype)
+        kx = ws.alloc((T, self.nh * self.dq), self.dtype)
+        vx = ws.alloc((T, self.nh * self.dv), self.dtype)
+        with ctx.prof("latent_expand"):
+            linear.matmul(ctx, rows[:, :self.rank], self.w_uk, kn)
+            linear.matmul(ctx, rows[:, :self.rank], self.w_uv2, vx)
+            ops.latent_expand_keys(kn, rows, kx, self.nh, self.d, self.rd, self.rank)
+        a = ws.alloc((T, self.nh * self.dv), self.dtype)
+        tiles = ctx.tiles(self.EXPANDED_TILE)
+        with ctx.prof("attn_latent"):
+            ops.masked_attn_tiled(q, a, kx, vx, None, tiles.seq, tiles.tok0, tiles.ntok, tiles.pos0, tiles.count, self.EXPANDED_TILE,
+                                  self.nh, self.nh, self.dq, self.dv, self.scale, self.mask, self.mask_size, None)
+        with ctx.prof("o_proj"):
+            linear.matmul(ctx, a, self.w_o, x, epilogue=linear.EPI_RESIDUAL if accumulate else linear.EPI_STORE,
+                          residual=x if accumulate else None, prefetch=ctx.weights_after)
 
     def forward(self, ctx, h, x, cache, accumulate=True):
         h = linear.as_tensor(h)
@@ -105,12 +139,14 @@ class LatentAttention(Part):
         u = ws.alloc((T, self.d_in), f32)
         with ctx.prof("latent_in_proj"):
             linear.matmul(ctx, h, self.w_in, u, prefetch=(self.w_o,))
+        own = not self.reads_foreign_cache
+        if own and self.d and not ctx.all_single and ctx.all_fresh:
+            return self._forward_own_keys(ctx, u, x, cache, accumulate)
         qf = ws.alloc((T, self.nh * self.dc), f32)
         table = ctx.page_table(cache.group)
-        own = not self.reads_foreign_cache
         with ctx.prof("latent_prepare"):
-            ops.latent_prepare(u, self.nh * self.dq, own, qf, self.norm_w, self.eps, ctx.tok_pos, ctx.tok_seq, table if own else None,
-                               cache.k if own else None, self.nh, self.d, self.rd, self.rank, self.freq, ctx.err)
+            ops.latent_prepare(u, self.nh * self.dq, own, qf, self.dc, self.rank, False, self.norm_w, self.eps, ctx.tok_pos, ctx.tok_seq,
+                               table if own else None, cache.k if own else None, self.nh, self.d, self.rd, self.rank, self.freq, ctx.err)
             if self.d:
                 ops.head_matmul(u, self.dq, self.w_ukt, qf, self.dc)
             else:

@@ -278,7 +278,7 @@ def test_latent_attention_path(H, d, rd, e, r, dtype):
         _, tok_seq = packed([n for _, _, n in live])
         tb = table[[s for s, _, _ in live]].contiguous()
         qf = torch.full((T, H * (r + rd)), float("nan"), device=DEV)
-        ops.latent_prepare(u, H * (d + rd), True, qf, f32(nw), eps, pos, tok_seq, tb, kv.k, H, d, rd, r, freq, err)
+        ops.latent_prepare(u, H * (d + rd), True, qf, r + rd, r, False, f32(nw), eps, pos, tok_seq, tb, kv.k, H, d, rd, r, freq, err)
         ops.head_matmul(u, d + rd, w_ukt, qf, r + rd)
         ol = torch.full((T, H * r), float("nan"), device=DEV)
         if phase == "prompt":
@@ -292,6 +292,20 @@ def test_latent_attention_path(H, d, rd, e, r, dtype):
         got = a.float().cpu().numpy()
         ref = np.concatenate([want[s][a0:a0 + n] for s, a0, n in live])
         assert np.abs(got - ref).max() < tol * max(1.0, np.abs(ref).max()), phase
+        if phase == "prompt":
+            # the same step with its own keys and values expanded per head (every sequence starts at position 0)
+            q2 = torch.full((T, H * (d + rd)), float("nan"), device=DEV)
+            rows = torch.full((T, r + rd), float("nan"), dtype=dtype, device=DEV)
+            ops.latent_prepare(u, H * (d + rd), True, q2, d + rd, d, True, f32(nw), eps, pos, tok_seq, tb, kv.k, H, d, rd, r, freq, err, row_out=rows)
+            c = rows[:, :r].float()
+            kn = (c @ torch.tensor(uk, dtype=torch.float32, device=DEV).T).to(dtype).contiguous()
+            vx = (c @ torch.tensor(uv, dtype=torch.float32, device=DEV).T).to(dtype).contiguous()
+            kx = torch.full((T, H * (d + rd)), float("nan"), dtype=dtype, device=DEV)
+            ops.latent_expand_keys(kn, rows, kx, H, d, rd, r)
+            tseq, ttok0, tntok, tpos0, count = make_tiles([n for _, _, n in live], [0] * len(live), 32)
+            a2 = torch.full((T, H * e), float("nan"), dtype=dtype, device=DEV)
+            ops.masked_attn_tiled(q2, a2, kx, vx, None, tseq, ttok0, tntok, tpos0, count, 32, H, H, d + rd, e, scale, ops.MASK_CAUSAL, 0, None)
+            assert np.abs(a2.float().cpu().numpy() - ref).max() < tol * max(1.0, np.abs(ref).max()), "own keys"
     assert int(err.item()) == 0
 
 
