@@ -344,7 +344,8 @@ __global__ void __launch_bounds__(TM_WARPS * 32)
 masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
                          const int32_t* __restrict__ page_table, int table_stride, int n_pages, const int32_t* __restrict__ tile_seq,
                          const int32_t* __restrict__ tile_tok0, const int32_t* __restrict__ tile_ntok, const int32_t* __restrict__ tile_pos0,
-                         int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* __restrict__ sink) {
+                         int H, int G, int dk, int dv, float scale, int mask, int mask_size, const float* __restrict__ sink,
+                         int n_splits, float* __restrict__ part) {
   extern __shared__ float tm_smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -363,7 +364,11 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
   const bool paged = page_table != nullptr;
   const int32_t* pages = paged ? page_table + (size_t)seq * table_stride : nullptr;
   const int k_pitch = paged ? dk : G * dk, v_pitch = paged ? dv : G * dv;
-  const int rows_total = ntok * grp, row_base = blockIdx.z * TM_ROWS;
+  // n_splits > 1: the pages a tile's rows see are dealt to n_splits blocks (blockIdx.z = row tile * n_splits + split); each
+  // leaves its rows' maximum, denominator and weighted values in `part` [token][head][split][2 + dv] and `masked_attn_fold`
+  // merges them: steps of one token a sequence whose query heads share few key heads
+  const int split = blockIdx.z % n_splits;
+  const int rows_total = ntok * grp, row_base = (blockIdx.z / n_splits) * TM_ROWS;
   if (row_base >= rows_total) return;
   const int rows_here = min(TM_ROWS, rows_total - row_base);
   const int last_pos = pos0 + (row_base + rows_here - 1) / grp, first_pos = pos0 + row_base / grp;
@@ -384,7 +389,12 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
 #pragma unroll
     for (int c = 0; c < NC; ++c) acc[r][c] = 0.f;
   }
-  const int kt_begin = first_key(first_pos, mask, mask_size) / PAGE, kt_end = last_pos / PAGE;
+  int kt_begin = first_key(first_pos, mask, mask_size) / PAGE, kt_end = last_pos / PAGE;
+  if (n_splits > 1) {
+    const int per = (kt_end - kt_begin + n_splits) / n_splits;
+    kt_begin += split * per;
+    kt_end = min(kt_end, kt_begin + per - 1);
+  }
   for (int kt = kt_begin; kt <= kt_end; ++kt) {
     const int page = paged ? pages[kt] : 0;
     const bool held = !paged || (page >= 0 && page < n_pages);
@@ -469,6 +479,16 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
     const int rr = row_base + warp * TM_RW + r;
     if (rr >= rows_total) continue;
     const int tok = rr / grp, head = g * grp + rr % grp;
+    if (n_splits > 1) {
+      float* dst = part + (((size_t)(tok0 + tok) * H + head) * n_splits + split) * (2 + dv);
+      if (lane == 0) { dst[0] = m[r]; dst[1] = l[r]; }
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const int d = lane + 32 * c;
+        if (d < dv) dst[2 + d] = acc[r][c];
+      }
+      continue;
+    }
     float lr = l[r], fix = 1.f;
     if (sink) {                                   // the sink: one more term of the denominator, no value
       const float sk = sink[head], mx = fmaxf(m[r], sk);
@@ -481,6 +501,32 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
       const int d = lane + 32 * c;
       if (d < dv) out[((size_t)(tok0 + tok) * H + head) * dv + d] = from_f32<TO>(acc[r][c] * inv);
     }
+  }
+}
+
+// out[t][h][:] from the splits' partial results [t][h][split][2 + dv]: maxima, denominators, weighted values; the sink joins here
+template <typename TO>
+__global__ void masked_attn_fold_kernel(const float* __restrict__ part, TO* __restrict__ out, const float* __restrict__ sink, int H, int dv,
+                                        int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const float* p = part + ((size_t)t * H + h) * n_splits * (2 + dv);
+  float M = sink ? sink[h] : -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, p[(size_t)s * (2 + dv)]);
+  float L = sink ? expf(sink[h] - M) : 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = p[(size_t)s * (2 + dv)];
+    if (ms != -INFINITY) L += p[(size_t)s * (2 + dv) + 1] * expf(ms - M);
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  for (int d = threadIdx.x; d < dv; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = p[(size_t)s * (2 + dv)];
+      if (ms != -INFINITY) acc = fmaf(p[(size_t)s * (2 + dv) + 2 + d], expf(ms - M), acc);
+    }
+    out[((size_t)t * H + h) * dv + d] = from_f32<TO>(acc * inv);
   }
 }
 
@@ -619,15 +665,21 @@ template <typename T, typename TO, int NC>
 static int launch_masked_tiled(const float* q, void* out, const void* kcache, const void* vcache, const int32_t* page_table, int table_stride,
                                int n_pages, const int32_t* tile_seq, const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0,
                                int n_tiles, int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                               const float* sink, cudaStream_t stream) {
+                               const float* sink, int n_splits, float* part, int n_tokens, cudaStream_t stream) {
   const size_t smem = ((size_t)TM_KEYS * (dk + 1) + (vcache ? (size_t)TM_KEYS * dv : 0) + (size_t)TM_ROWS * dk + (size_t)TM_ROWS * TM_KEYS) * sizeof(float);
   EL_REFUSE(smem <= 227 * 1024, "masked_attn_tiled: heads of %d / %d need %zu bytes of shared memory", dk, dv, smem);
   auto kern = masked_attn_tiled_kernel<T, TO, NC>;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   const int grp = H / G;
-  const dim3 grid(n_tiles, G, (max_tile_tokens * grp + TM_ROWS - 1) / TM_ROWS);
-  launch_pdl(0, kern, grid, dim3(TM_WARPS * 32), smem, stream, q, (TO*)out, (const T*)kcache, (const T*)vcache, page_table, table_stride, n_pages,
-             tile_seq, tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, mask, mask_size, sink);
+  const dim3 grid(n_tiles, G, ((max_tile_tokens * grp + TM_ROWS - 1) / TM_ROWS) * n_splits);
+  const int bit = pdl_bit_for_tokens(n_tokens);
+  launch_pdl(bit, kern, grid, dim3(TM_WARPS * 32), smem, stream, q, (TO*)out, (const T*)kcache, (const T*)vcache, page_table, table_stride, n_pages,
+             tile_seq, tile_tok0, tile_ntok, tile_pos0, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part);
+  if (n_splits > 1) {
+    if (cudaGetLastError() != cudaSuccess) return 0;   // (the caller reports it)
+    launch_pdl(bit, masked_attn_fold_kernel<TO>, dim3(n_tokens, H), dim3(dv >= 256 ? 256 : 128), (size_t)0, stream, (const float*)part, (TO*)out, sink, H, dv,
+               n_splits);
+  }
   return 0;
 }
 
@@ -635,13 +687,14 @@ extern "C" int edgelm_masked_attn_tiled(const float* q, void* out, int out_dtype
                                         const int32_t* page_table, int table_stride, int n_pages, const int32_t* tile_seq,
                                         const int32_t* tile_tok0, const int32_t* tile_ntok, const int32_t* tile_pos0, int n_tiles,
                                         int max_tile_tokens, int H, int G, int dk, int dv, float scale, int mask, int mask_size,
-                                        const float* sink, cudaStream_t stream) {
+                                        const float* sink, int n_splits, float* part, int n_tokens, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
+  EL_REFUSE(n_splits >= 1 && n_splits <= 64 && (n_splits == 1 || part != nullptr) && n_tokens > 0, "masked_attn_tiled: %d splits", n_splits);
   if (masked_common_check("masked_attn_tiled", H, G, dk, dv, mask, mask_size, dtype, out_dtype)) return -1;
   EL_REFUSE(n_tiles > 0 && max_tile_tokens > 0 && G <= 65535, "masked_attn_tiled: bad tile counts");
   EL_REFUSE(vcache != nullptr || dv <= dk, "masked_attn_tiled: values of %d inside keys of %d", dv, dk);
   int rc = 0;
-#define EL_MT2(T, TO, NC) rc = launch_masked_tiled<T, TO, NC>(q, out, kcache, vcache, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, mask, mask_size, sink, stream)
+#define EL_MT2(T, TO, NC) rc = launch_masked_tiled<T, TO, NC>(q, out, kcache, vcache, page_table, table_stride, n_pages, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, H, G, dk, dv, scale, mask, mask_size, sink, n_splits, part, n_tokens, stream)
 #define EL_MT(NC) do { if (dtype == DT_F32) EL_MT2(float, float, NC); else if (out_dtype == DT_F32) EL_MT2(__nv_bfloat16, float, NC); else EL_MT2(__nv_bfloat16, __nv_bfloat16, NC); } while (0)
   if (dv <= 32) EL_MT(1); else if (dv <= 64) EL_MT(2); else if (dv <= 128) EL_MT(4); else if (dv <= 256) EL_MT(8); else EL_MT(16);
 #undef EL_MT

@@ -728,10 +728,12 @@ def masked_attn(q, out, kcache, vcache, tok_pos, tok_seq, page_table, nh, nkv, d
 
 
 def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, tile_ntok, tile_pos0, n_tiles, max_tile_tokens, nh, nkv,
-                      dk, dv, scale, mask, mask_size, sink):
+                      dk, dv, scale, mask, mask_size, sink, n_splits=1, part=None):
     """`masked_attn` for prompt steps: the step's tokens come as tiles (runs of at most `max_tile_tokens` consecutive tokens of
     one sequence); a page of keys and values is staged once for all the rows of a tile.  `page_table` None: `kcache` [T, nkv dk]
-    and `vcache` [T, nkv dv] are the step's own keys and values, and every sequence of the step starts at position 0."""
+    and `vcache` [T, nkv dv] are the step's own keys and values, and every sequence of the step starts at position 0.
+    `n_splits` > 1: the pages that a tile sees are dealt to so many blocks, whose partial results go through `part` (float32,
+    T nh n_splits (2 + dv) values) and are merged by a second launch: for steps of few tokens over long sequences."""
     _f32(q, "q")
     T = q.shape[0]
     _need(q.shape == (T, nh * dk) and out.is_contiguous() and out.shape == (T, nh * dv), "masked_attn_tiled: shapes")
@@ -742,12 +744,15 @@ def masked_attn_tiled(q, out, kcache, vcache, page_table, tile_seq, tile_tok0, t
         _need(vcache is not None and kcache.is_contiguous() and vcache.is_contiguous() and kcache.dtype == vcache.dtype and
               kcache.shape == (T, nkv * dk) and vcache.shape == (T, nkv * dv), "masked_attn_tiled: the step's own keys and values")
     _need(sink is None or (sink.dtype == torch.float32 and sink.is_contiguous() and sink.numel() == nh), "masked_attn_tiled: sink")
+    _need(n_splits == 1 or (part is not None and part.dtype == torch.float32 and part.is_contiguous() and part.numel() >= T * nh * n_splits * (2 + dv)),
+          "masked_attn_tiled: room for the splits' partial results")
     for t, n in ((tile_seq, "tile_seq"), (tile_tok0, "tile_tok0"), (tile_ntok, "tile_ntok"), (tile_pos0, "tile_pos0")):
         _i32(t, n)
     _check(lib().edgelm_masked_attn_tiled(_p(q), _p(out), _dt(out), _p(kcache), _p(vcache), _dt(kcache), _p(page_table),
                                           page_table.stride(0) if page_table is not None else 0, kcache.shape[0] if page_table is not None else 0,
                                           _p(tile_seq), _p(tile_tok0), _p(tile_ntok), _p(tile_pos0), int(n_tiles),
-                                          int(max_tile_tokens), nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0), _p(sink), _stream()))
+                                          int(max_tile_tokens), nh, nkv, dk, dv, ctypes.c_float(scale), int(mask), int(mask_size or 0), _p(sink),
+                                          int(n_splits), _p(part), T, _stream()), launches=2 if n_splits > 1 else 1)
 
 
 # ----------------------------------------------------------------------------- gated delta rule

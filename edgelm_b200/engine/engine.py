@@ -251,7 +251,9 @@ class Engine:
             return False
         if any(t not in ctx._tiles for t in self.buffers.tile_sizes):   # (the model's own list, taken when the buffers were made)
             return False
-        key = (shape, n_want, ctx.all_fresh)     # (a part may run a step of first tokens another way: `StepContext.all_fresh`)
+        # (a part may run a step of first tokens another way, `StepContext.all_fresh`: such a step and one of the same shape
+        # that goes on from earlier tokens are two graphs)
+        key = (shape, n_want) if ctx.all_fresh else (shape, n_want, "continued")
         g = self._step_graphs.get(key)
         if g is None:
             self._step_seen[key] = self._step_seen.get(key, 0) + 1

@@ -23,7 +23,7 @@ from ..config.base import ConfigError
 from ..csrc import ops
 from . import linear
 from .base import KVNeed, Part, as_matrix, as_vector, nbytes
-from .masked_attention import MASKS, most_keys, read_mask
+from .masked_attention import MASKS, SHARED_KEYS_MIN_GROUP, decode_splits, most_keys, read_mask, single_token_tiles, splits_room
 from .registry import register_mixer
 from .rope import rotary_frequencies
 
@@ -103,7 +103,7 @@ class LatentAttention(Part):
         absorbed = nbytes((n_tokens, self.nh * self.dc), f32) + nbytes((n_tokens, self.nh * self.rank), f32)
         expanded = (nbytes((n_tokens, self.nh * self.dq), f32) + nbytes((n_tokens, self.dc), self.dtype) + nbytes((n_tokens, self.nh * self.d), self.dtype) +
                     nbytes((n_tokens, self.nh * self.dq), self.dtype) + nbytes((n_tokens, self.nh * self.dv), self.dtype))
-        return (nbytes((n_tokens, self.d_in), f32) + max(absorbed, expanded) +
+        return (nbytes((n_tokens, self.d_in), f32) + max(absorbed + splits_room(n_seqs, self.nh, self.rank), expanded) +
                 nbytes((n_tokens, self.nh * self.dv), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype))
 
     def _forward_own_keys(self, ctx, u, x, cache, accumulate):
@@ -153,7 +153,13 @@ class LatentAttention(Part):
                 qf.view(T, self.nh, self.dc)[:, :, :self.rank].zero_()
         ol = ws.alloc((T, self.nh * self.rank), f32)
         with ctx.prof("attn_latent"):
-            if ctx.all_single:
+            if ctx.all_single and self.nh >= SHARED_KEYS_MIN_GROUP:     # a row of the latent is staged once for all the heads
+                splits = decode_splits(ctx, 1, self.nh, self.mask, self.mask_size)
+                part = ws.alloc((T * self.nh * splits * (2 + self.rank),), f32) if splits > 1 else None
+                tseq, ttok0, tntok, tpos0 = single_token_tiles(ctx)
+                ops.masked_attn_tiled(qf, ol, cache.k, None, table, tseq, ttok0, tntok, tpos0, T, 1, self.nh, 1, self.dc, self.rank, self.scale,
+                                      self.mask, self.mask_size, None, n_splits=splits, part=part)
+            elif ctx.all_single:
                 ops.masked_attn(qf, ol, cache.k, None, ctx.tok_pos, ctx.tok_seq, table, self.nh, 1, self.dc, self.rank, self.scale,
                                 self.mask, self.mask_size, None, most_keys(self.mask, self.mask_size))
             else:

@@ -45,6 +45,38 @@ def most_keys(mask, size):
     return size if mask != ops.MASK_CAUSAL else 1 << 30
 
 
+# Steps of one token a sequence: with at least so many query heads to a key head the tiled kernel is used (a tile = one
+# token, its rows = the heads that share the key head, so a key row is staged once for all of them), its pages dealt to
+# several blocks; with fewer, a block per (token, head) whose warps share the keys.
+SHARED_KEYS_MIN_GROUP = 8
+MAX_SPLITS = 32
+_ones = {}
+
+
+def single_token_tiles(ctx):
+    """The tiles of a step of one token a sequence, from what the step's metadata holds already: (row of the page table,
+    packed row, token count, position) per tile."""
+    key = str(ctx.device)
+    if key not in _ones or _ones[key].numel() < ctx.n_seqs:
+        _ones[key] = torch.ones(max(256, 2 * ctx.n_seqs), dtype=torch.int32, device=ctx.device)
+    return ctx.seq_index, ctx.seq_index, _ones[key][:ctx.n_seqs], ctx.tok_pos
+
+
+def decode_splits(ctx, n_kv_heads, group, mask, mask_size):
+    """Blocks that share a token's pages in the tiled kernel: about two blocks an SM, at most a block a page of the mask."""
+    tiles = max(1, ctx.n_seqs * n_kv_heads * ((group + 31) // 32))
+    splits = min(MAX_SPLITS, max(1, (2 * ctx.n_sms + tiles - 1) // tiles))
+    if mask != ops.MASK_CAUSAL:
+        splits = min(splits, (mask_size + 63) // 64 + 1)
+    return splits
+
+
+def splits_room(n_seqs, n_heads, dv):
+    """Bytes of the splits' partial results for a step of `n_seqs` single tokens (sequences x splits stays under 2 SMs' worth
+    of blocks plus the sequences themselves; 600 covers devices of up to 300 SMs)."""
+    return nbytes(((600 + n_seqs) * n_heads * (2 + dv),), torch.float32)
+
+
 @register_mixer("masked_attention")
 class MaskedAttention(Part):
     graph_safe = True
@@ -118,7 +150,8 @@ class MaskedAttention(Part):
 
     def workspace_bytes(self, n_tokens, n_seqs):
         return (nbytes((n_tokens, self.d_qkv), torch.float32) + nbytes((n_tokens, self.nh * self.dk), torch.float32) +
-                nbytes((n_tokens, self.nh * self.dv), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype))
+                nbytes((n_tokens, self.nh * self.dv), self.dtype) + nbytes((n_tokens, self.hidden), self.dtype) +
+                splits_room(n_seqs, self.nh, self.dv))
 
     def forward(self, ctx, h, x, cache, accumulate=True):
         h = linear.as_tensor(h)
@@ -133,7 +166,13 @@ class MaskedAttention(Part):
                               self.rot, self.interleaved, self.freq, ctx.err)
         a = ws.alloc((T, self.nh * self.dv), self.dtype)
         with ctx.prof("attn_masked"):
-            if ctx.all_single:
+            if ctx.all_single and self.nh // self.nkv >= SHARED_KEYS_MIN_GROUP:
+                splits = decode_splits(ctx, self.nkv, self.nh // self.nkv, self.mask, self.mask_size)
+                part = ws.alloc((T * self.nh * splits * (2 + self.dv),), torch.float32) if splits > 1 else None
+                tseq, ttok0, tntok, tpos0 = single_token_tiles(ctx)
+                ops.masked_attn_tiled(q, a, cache.k, cache.v, table, tseq, ttok0, tntok, tpos0, T, 1, self.nh, self.nkv, self.dk, self.dv,
+                                      self.scale, self.mask, self.mask_size, self.sink, n_splits=splits, part=part)
+            elif ctx.all_single:
                 ops.masked_attn(q, a, cache.k, cache.v, ctx.tok_pos, ctx.tok_seq, table, self.nh, self.nkv, self.dk, self.dv, self.scale,
                                 self.mask, self.mask_size, self.sink, most_keys(self.mask, self.mask_size))
             else:

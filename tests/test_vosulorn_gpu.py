@@ -188,8 +188,8 @@ def test_a_far_key_decides(tmp_path):
     left out or a latent row read from the wrong place moves the logits by their own size, in prompts and in decoding."""
     from edgelm_b200.engine.engine import Engine
     cfg = {"architecture": "Vosulorn", "vocab": 120, "width": 48, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0}, "layers": [
-        M.attention(4, 2, 16, 16, 0.25, {"base": 5000.0, "dims": 8}, 96, None),
-        M.latent(3, 16, 8, 12, 24, 0.25, 5000.0, M.moe(3, 2, 20)),
+        M.attention(8, 1, 16, 16, 0.25, {"base": 5000.0, "dims": 8}, 96, None),     # (eight heads to a key head: decoding shares the staged keys)
+        M.latent(8, 16, 8, 12, 24, 0.25, 5000.0, M.moe(3, 2, 20)),
         M.latent(2, 8, 8, 20, 24, 0.3, 5000.0, None, kv_from=1)]}
     W = M.tensors_for(cfg, 77)
     for name in ("l0.mix.q", "l0.mix.k", "l1.mix.q", "l1.mix.dkv", "l2.mix.q"):

@@ -203,6 +203,14 @@ def test_attention_with_a_key_range(H, G, dk, dv, kind, size, with_sink, dtype):
         got = out.float().cpu().numpy()
         ref = np.stack([want[s][p].reshape(H * dv) for s, p in live])
         assert np.abs(got - ref).max() < tol * max(1.0, np.abs(ref).max()), ("single", back)
+        # the same tokens as tiles of one token, their pages dealt to 1, 3 and 5 blocks whose results a second launch merges
+        for splits in (1, 3, 5):
+            out2 = torch.full((len(live), H * dv), float("nan"), dtype=dtype, device=DEV)
+            part = torch.full((len(live) * H * splits * (2 + dv),), float("nan"), device=DEV)
+            n = len(live)
+            ops.masked_attn_tiled(q, out2, kv.k, kv.v, table[[s for s, _ in live]].contiguous(), i32(list(range(n))), i32(list(range(n))), i32([1] * n),
+                                  i32([p for _, p in live]), n, 1, H, G, dk, dv, scale, mk, ms, sk, n_splits=splits, part=part)
+            assert np.abs(out2.float().cpu().numpy() - ref).max() < tol * max(1.0, np.abs(ref).max()), ("single, split", back, splits)
 
 
 @pytest.mark.parametrize("interleaved", [True, False])
