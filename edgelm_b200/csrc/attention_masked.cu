@@ -164,25 +164,27 @@ __global__ void latent_expand_keys_kernel(const T* __restrict__ kn, const T* __r
 }
 
 // out[t][h * out_hs + n] = sum_k a[t][h * a_hs + k] * w[h][n][k], float32 sums; a: float32 rows of lda floats, out: rows of ldo values.
-constexpr int HM_TT = 32, HM_TN = 64, HM_KC = 32;
-template <typename TW, typename TO>
+// Tiles of 32 tokens x TN columns (TN 64, or 16 when the step has few tokens: four times the blocks), K in steps of 32.
+constexpr int HM_TT = 32, HM_KC = 32;
+template <typename TW, typename TO, int TN>
 __global__ void __launch_bounds__(256)
 head_matmul_kernel(const float* __restrict__ a, int lda, int a_hs, const TW* __restrict__ w, TO* __restrict__ out, int ldo,
                    int out_hs, int n_tokens, int K, int N) {
   pdl_launch_dependents();
   pdl_wait();
+  constexpr int NJ = TN / 16;      // columns a thread
   __shared__ float As[HM_TT][HM_KC + 1];
-  __shared__ float Ws[HM_TN][HM_KC + 1];
-  const int h = blockIdx.z, t0 = blockIdx.x * HM_TT, n0 = blockIdx.y * HM_TN;
-  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;     // 16 column groups of 4, 16 row groups of 2
+  __shared__ float Ws[TN][HM_KC + 1];
+  const int h = blockIdx.z, t0 = blockIdx.x * HM_TT, n0 = blockIdx.y * TN;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;     // 16 column groups, 16 row groups of 2
   const TW* wh = w + (size_t)h * N * K;
-  float acc[2][4] = {};
+  float acc[2][NJ] = {};
   for (int k0 = 0; k0 < K; k0 += HM_KC) {
     for (int i = threadIdx.x; i < HM_TT * HM_KC; i += 256) {
       const int r = i / HM_KC, k = i - r * HM_KC;
       As[r][k] = (t0 + r < n_tokens && k0 + k < K) ? a[(size_t)(t0 + r) * lda + (size_t)h * a_hs + k0 + k] : 0.f;
     }
-    for (int i = threadIdx.x; i < HM_TN * HM_KC; i += 256) {
+    for (int i = threadIdx.x; i < TN * HM_KC; i += 256) {
       const int r = i / HM_KC, k = i - r * HM_KC;
       Ws[r][k] = (n0 + r < N && k0 + k < K) ? to_f32(wh[(size_t)(n0 + r) * K + k0 + k]) : 0.f;
     }
@@ -191,7 +193,7 @@ head_matmul_kernel(const float* __restrict__ a, int lda, int a_hs, const TW* __r
     for (int k = 0; k < HM_KC; ++k) {
       const float a0 = As[ty * 2][k], a1 = As[ty * 2 + 1][k];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < NJ; ++j) {
         const float wv = Ws[tx + 16 * j][k];
         acc[0][j] = fmaf(a0, wv, acc[0][j]);
         acc[1][j] = fmaf(a1, wv, acc[1][j]);
@@ -202,7 +204,7 @@ head_matmul_kernel(const float* __restrict__ a, int lda, int a_hs, const TW* __r
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < NJ; ++j) {
       const int t = t0 + ty * 2 + i, n = n0 + tx + 16 * j;
       if (t < n_tokens && n < N) out[(size_t)t * ldo + (size_t)h * out_hs + n] = from_f32<TO>(acc[i][j]);
     }
@@ -339,6 +341,42 @@ masked_attn_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* _
 // scores and value dimensions for the weighted sum.  Row r sees key p iff first[r] <= p <= its own position.
 constexpr int TM_RW = 4, TM_WARPS = 8, TM_ROWS = TM_RW * TM_WARPS, TM_KEYS = PAGE;
 
+// PAGE rows of n values from global memory (row pitch `src_pitch`) into shared memory as float32 (row pitch `dst_pitch`); rows from
+// `valid` on become zeros.  16 bytes a load where the rows allow it: a thread then has a few loads in flight instead of
+// one per value.
+template <typename T>
+__device__ __forceinline__ void stage_rows(float* __restrict__ dst, int dst_pitch, const T* __restrict__ src, int src_pitch, int n, int valid) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const bool vec = n % V == 0 && src_pitch % V == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  if (vec) {
+    const int per_row = n / V;
+#pragma unroll 4
+    for (int i = threadIdx.x; i < PAGE * per_row; i += blockDim.x) {
+      const int j = i / per_row, d = (i - j * per_row) * V;
+      float* o = dst + j * dst_pitch + d;
+      if (j < valid) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)j * src_pitch + d);
+        if constexpr (sizeof(T) == 4) {
+          o[0] = __uint_as_float(raw.x); o[1] = __uint_as_float(raw.y); o[2] = __uint_as_float(raw.z); o[3] = __uint_as_float(raw.w);
+        } else {
+          o[0] = __uint_as_float(raw.x << 16); o[1] = __uint_as_float(raw.x & 0xffff0000u);
+          o[2] = __uint_as_float(raw.y << 16); o[3] = __uint_as_float(raw.y & 0xffff0000u);
+          o[4] = __uint_as_float(raw.z << 16); o[5] = __uint_as_float(raw.z & 0xffff0000u);
+          o[6] = __uint_as_float(raw.w << 16); o[7] = __uint_as_float(raw.w & 0xffff0000u);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < V; ++q) o[q] = 0.f;
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < PAGE * n; i += blockDim.x) {
+      const int j = i / n, d = i - j * n;
+      dst[j * dst_pitch + d] = j < valid ? to_f32(src[(size_t)j * src_pitch + d]) : 0.f;
+    }
+  }
+}
+
 template <typename T, typename TO, int NC>    // NC = ceil(dv / 32): value dimensions a lane owns
 __global__ void __launch_bounds__(TM_WARPS * 32)
 masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, const T* __restrict__ kcache, const T* __restrict__ vcache,
@@ -402,17 +440,8 @@ masked_attn_tiled_kernel(const float* __restrict__ q, TO* __restrict__ out, cons
     const T* kp = kcache + first_row * dk;
     const int valid = held ? min(PAGE, last_pos + 1 - kt * PAGE) : 0;   // rows of the page that hold this block's keys
     __syncthreads();
-    for (int i = threadIdx.x; i < PAGE * dk; i += blockDim.x) {
-      const int j = i / dk, d = i - j * dk;
-      Ks[j * ks + d] = j < valid ? to_f32(kp[(size_t)j * k_pitch + d]) : 0.f;   // what lies behind is not this sequence's: never let it in
-    }
-    if (own_v) {
-      const T* vp = vcache + first_row * dv;
-      for (int i = threadIdx.x; i < PAGE * dv; i += blockDim.x) {
-        const int j = i / dv, d = i - j * dv;
-        Vs[i] = j < valid ? to_f32(vp[(size_t)j * v_pitch + d]) : 0.f;
-      }
-    }
+    stage_rows<T>(Ks, ks, kp, k_pitch, dk, valid);      // what lies behind `valid` is not this sequence's: never let it in
+    if (own_v) stage_rows<T>(Vs, dv, vcache + first_row * dv, v_pitch, dv, valid);
     __syncthreads();
     const int base = kt * PAGE;
     int any_hi = -1, any_lo = 0x7fffffff;
@@ -599,9 +628,11 @@ extern "C" int edgelm_head_matmul(const float* a, int lda, int a_hs, const void*
                                   int n_tokens, int H, int K, int N, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && H > 0 && K > 0 && N > 0 && H <= 65535, "head_matmul: bad sizes heads %d, K %d, N %d", H, K, N);
-  const dim3 grid((n_tokens + HM_TT - 1) / HM_TT, (N + HM_TN - 1) / HM_TN, H), block(256);
+  const int tn = n_tokens <= 64 ? 16 : 64;
+  const dim3 grid((n_tokens + HM_TT - 1) / HM_TT, (N + tn - 1) / tn, H), block(256);
   const int bit = pdl_bit_for_tokens(n_tokens);
-#define EL_HM(TW, TO) launch_pdl(bit, head_matmul_kernel<TW, TO>, grid, block, (size_t)0, stream, a, lda, a_hs, (const TW*)w, (TO*)out, ldo, out_hs, n_tokens, K, N)
+#define EL_HM(TW, TO) do { if (tn == 16) launch_pdl(bit, head_matmul_kernel<TW, TO, 16>, grid, block, (size_t)0, stream, a, lda, a_hs, (const TW*)w, (TO*)out, ldo, out_hs, n_tokens, K, N); \
+    else launch_pdl(bit, head_matmul_kernel<TW, TO, 64>, grid, block, (size_t)0, stream, a, lda, a_hs, (const TW*)w, (TO*)out, ldo, out_hs, n_tokens, K, N); } while (0)
   if (w_dtype == DT_F32 && out_dtype == DT_F32) EL_HM(float, float);
   else if (w_dtype == DT_BF16 && out_dtype == DT_F32) EL_HM(__nv_bfloat16, float);
   else if (w_dtype == DT_BF16 && out_dtype == DT_BF16) EL_HM(__nv_bfloat16, __nv_bfloat16);

@@ -26,7 +26,7 @@ delta_prepare_kernel(float* __restrict__ qkv, int C, const float* __restrict__ u
   pdl_wait();
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, NW = blockDim.x >> 5;
   float* row = qkv + (size_t)t * C;
-  for (int v = warp; v < 2 * G; v += NW) {          // the vectors: G query heads, then G key heads
+  for (int v = blockIdx.y * NW + warp; v < 2 * G; v += gridDim.y * NW) {          // the vectors: G query heads, then G key heads
     float* x = row + (size_t)v * d;
     float ss = 0.f;
     for (int i = lane; i < d; i += 32) ss = fmaf(x[i], x[i], ss);
@@ -35,7 +35,7 @@ delta_prepare_kernel(float* __restrict__ qkv, int C, const float* __restrict__ u
     for (int i = lane; i < d; i += 32) x[i] *= inv;
   }
   const float* ur = u + (size_t)t * ldu;
-  for (int h = threadIdx.x; h < H; h += blockDim.x) {
+  for (int h = blockIdx.y * blockDim.x + threadIdx.x; h < H; h += gridDim.y * blockDim.x) {
     bg[(size_t)t * 2 * H + h] = 1.0f / (1.0f + expf(-ur[b_off + h]));
     bg[(size_t)t * 2 * H + H + h] = expf(-expf(A_log[h]) * dr_softplus(ur[a_off + h] + dt_bias[h]));
   }
@@ -158,7 +158,8 @@ extern "C" int edgelm_delta_prepare(float* qkv, int C, const float* u, int ldu, 
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && H > 0 && G > 0 && H % G == 0 && d > 0 && e > 0 && C == 2 * G * d + H * e, "delta_prepare: sizes do not fit (heads %d over %d, %d x %d, channels %d)", H, G, d, e, C);
   EL_REFUSE(b_off >= 0 && a_off >= 0 && b_off + H <= ldu && a_off + H <= ldu, "delta_prepare: rows of %d values are too short", ldu);
-  launch_pdl(pdl_bit_for_tokens(n_tokens), delta_prepare_kernel, dim3(n_tokens), dim3(128), (size_t)0, stream, qkv, C, u, ldu, b_off, a_off, A_log,
+  const int vec_blocks = n_tokens >= 256 ? 1 : (2 * G + 3) / 4;    // a step of few tokens: a warp a vector
+  launch_pdl(pdl_bit_for_tokens(n_tokens), delta_prepare_kernel, dim3(n_tokens, vec_blocks), dim3(128), (size_t)0, stream, qkv, C, u, ldu, b_off, a_off, A_log,
              dt_bias, bg, H, G, d, unit_eps, q_scale);
   EL_LAUNCH_CHECK("delta_prepare");
   return 0;

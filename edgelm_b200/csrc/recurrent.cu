@@ -68,7 +68,7 @@ __global__ void conv_silu_kernel(const float* __restrict__ u, int ldu, int off, 
   const int t0 = seq_tok0[s];
   const int k = t - t0;
   const float* st = state + (size_t)seq_slot[s] * (taps - 1) * C;
-  for (int c = threadIdx.x; c < C; c += blockDim.x) {
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {   // (few tokens: several blocks a token)
     float acc = b[c];
     for (int j = 0; j < taps; ++j) {
       const int r = k - (taps - 1) + j;
@@ -504,7 +504,8 @@ extern "C" int edgelm_conv_silu(const float* u, int ldu, int off, const float* w
                                 int C, int taps, int update_state, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   EL_REFUSE(n_tokens > 0 && n_seqs > 0 && C > 0 && taps >= 1 && off >= 0 && off + C <= ldu, "conv_silu: bad sizes C=%d taps=%d", C, taps);
-  launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps);
+  const int col_blocks = n_tokens >= 256 ? 1 : (C + 4 * row_threads(C) - 1) / (4 * row_threads(C));   // a step of few tokens: a block per 4 channels a thread
+  launch_pdl(pdl_bit_for_tokens(n_tokens), conv_silu_kernel, dim3(n_tokens, col_blocks), dim3(row_threads(C)), (size_t)(0), stream, u, ldu, off, w, b, state, out, tok_seq, seq_tok0, seq_slot, C, taps);
   EL_LAUNCH_CHECK("conv_silu");
   if (taps > 1 && update_state) {
     launch_pdl(pdl_bit_for_tokens(n_tokens), conv_state_update_kernel, dim3(dim3(n_seqs, (C + 255) / 256)), dim3(256), (size_t)(0), stream, u, ldu, off, state, seq_tok0, seq_slot, C, taps);
