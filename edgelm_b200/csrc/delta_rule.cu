@@ -104,34 +104,47 @@ delta_scan_kernel(const float* __restrict__ qkv, int C, const float* __restrict_
     __syncthreads();
     const float* b = sm + (c & 1) * STAGE;
     const int nt = min(DS_TC, n - c * DS_TC);
-    for (int tt = 0; tt < nt; ++tt) {
+    // a token's inputs are read from shared memory one token ahead of their use, so that no read's latency stands in the
+    // chain from one token's state to the next
+    constexpr int NV = RPT / 4;
+    float4 k4[NV], q4[NV], k4n[NV], q4n[NV];
+    float beta, dec, v, beta_n, dec_n, v_n;
+    auto fetch = [&](int tt, float4 (&kd)[NV], float4 (&qd)[NV], float& bt, float& dc, float& vv) {
       const float* qs = b + tt * DP + sub * RPT;
       const float* kk = b + DS_TC * DP + tt * DP + sub * RPT;
-      const float beta = b[2 * DS_TC * DP + DS_TC * DS_COLS + tt], dec = b[2 * DS_TC * DP + DS_TC * DS_COLS + DS_TC + tt];
-      const float v = b[2 * DS_TC * DP + tt * DS_COLS + colb];
-      float kr[RPT];
-      float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-      for (int r = 0; r < RPT; r += 4) {
-        const float4 k4 = *reinterpret_cast<const float4*>(kk + r);
-        kr[r] = k4.x; kr[r + 1] = k4.y; kr[r + 2] = k4.z; kr[r + 3] = k4.w;
+      for (int i = 0; i < NV; ++i) { kd[i] = *reinterpret_cast<const float4*>(kk + 4 * i); qd[i] = *reinterpret_cast<const float4*>(qs + 4 * i); }
+      bt = b[2 * DS_TC * DP + DS_TC * DS_COLS + tt];
+      dc = b[2 * DS_TC * DP + DS_TC * DS_COLS + DS_TC + tt];
+      vv = b[2 * DS_TC * DP + tt * DS_COLS + colb];
+    };
+    fetch(0, k4n, q4n, beta_n, dec_n, v_n);
+    for (int tt = 0; tt < nt; ++tt) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) { k4[i] = k4n[i]; q4[i] = q4n[i]; }
+      beta = beta_n; dec = dec_n; v = v_n;
+      if (tt + 1 < nt) fetch(tt + 1, k4n, q4n, beta_n, dec_n, v_n);
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int r = 4 * i;
         S[r] *= dec; S[r + 1] *= dec; S[r + 2] *= dec; S[r + 3] *= dec;
-        a0 = fmaf(S[r], k4.x, a0); a1 = fmaf(S[r + 1], k4.y, a1); a0 = fmaf(S[r + 2], k4.z, a0); a1 = fmaf(S[r + 3], k4.w, a1);
+        a0 = fmaf(S[r], k4[i].x, a0); a1 = fmaf(S[r + 1], k4[i].y, a1); a2 = fmaf(S[r + 2], k4[i].z, a2); a3 = fmaf(S[r + 3], k4[i].w, a3);
       }
-      float ks = a0 + a1;
+      float ks = (a0 + a1) + (a2 + a3);
       ks += __shfl_xor_sync(0xffffffffu, ks, 1);
       ks += __shfl_xor_sync(0xffffffffu, ks, 2);
       ks += __shfl_xor_sync(0xffffffffu, ks, 4);
       const float uu = beta * (v - ks);
-      a0 = 0.f; a1 = 0.f;
+      a0 = 0.f; a1 = 0.f; a2 = 0.f; a3 = 0.f;
 #pragma unroll
-      for (int r = 0; r < RPT; r += 4) {
-        const float4 q4 = *reinterpret_cast<const float4*>(qs + r);
-        S[r] = fmaf(kr[r], uu, S[r]); S[r + 1] = fmaf(kr[r + 1], uu, S[r + 1]);
-        S[r + 2] = fmaf(kr[r + 2], uu, S[r + 2]); S[r + 3] = fmaf(kr[r + 3], uu, S[r + 3]);
-        a0 = fmaf(S[r], q4.x, a0); a1 = fmaf(S[r + 1], q4.y, a1); a0 = fmaf(S[r + 2], q4.z, a0); a1 = fmaf(S[r + 3], q4.w, a1);
+      for (int i = 0; i < NV; ++i) {
+        const int r = 4 * i;
+        S[r] = fmaf(k4[i].x, uu, S[r]); S[r + 1] = fmaf(k4[i].y, uu, S[r + 1]);
+        S[r + 2] = fmaf(k4[i].z, uu, S[r + 2]); S[r + 3] = fmaf(k4[i].w, uu, S[r + 3]);
+        a0 = fmaf(S[r], q4[i].x, a0); a1 = fmaf(S[r + 1], q4[i].y, a1); a2 = fmaf(S[r + 2], q4[i].z, a2); a3 = fmaf(S[r + 3], q4[i].w, a3);
       }
-      float ov = a0 + a1;
+      float ov = (a0 + a1) + (a2 + a3);
       ov += __shfl_xor_sync(0xffffffffu, ov, 1);
       ov += __shfl_xor_sync(0xffffffffu, ov, 2);
       ov += __shfl_xor_sync(0xffffffffu, ov, 4);
