@@ -31,10 +31,10 @@ def _vosulorn(vocab, width, ff, groups_of_layers, heads, kv_heads, kv_rank, rot_
     delta = {"type": "delta", "mlp": moe, "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "conv": 4}}
     latent = {"type": "latent_attention", "mlp": moe, "mixer": {
         "heads": heads, "dim": 64, "rot_dim": rot_dim, "vdim": 64, "kv_rank": kv_rank, "scale": (64 + rot_dim) ** -0.5,
-        "rot": {"base": 500000.0, "dims": rot_dim}}}
+        "rot": {"base": 1000000.0, "dims": rot_dim}}}
     attn = {"type": "attention", "mlp": moe, "mixer": {
         "heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": chunk},
-        "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}}
+        "rot": {"base": 250000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}}}
     return {"architecture": "Vosulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
             "max_positions": 8192, "layers": [delta, latent, delta, attn] * groups_of_layers}
 
